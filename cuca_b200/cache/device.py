@@ -32,14 +32,14 @@ def plan_groups(cache_needs: dict, kv_tokens: int, block_size: int, max_sequence
         kv = cache_needs[cid].kv
         if kv is None:
             continue
-        by_key.setdefault((kv.n_kv_heads, kv.head_dim, kv.window), []).append(cid)
+        by_key.setdefault((kv.n_kv_heads, kv.head_dim, kv.window, kv.v_head_dim), []).append(cid)
     full = -(-kv_tokens // block_size)
     groups = []
-    for (nkv, d, window), ids in by_key.items():
+    for (nkv, d, window, vd), ids in by_key.items():
         n = full
         if window is not None and window_pools == "sized":
             n = min(full, max_sequences * (-(-(window - 1 + max_step_tokens) // block_size) + 2))
-        groups.append(GroupLayout(nkv, d, window, tuple(ids), max(1, n)))
+        groups.append(GroupLayout(nkv, d, window, tuple(ids), max(1, n), vd))
     return groups
 
 
@@ -52,7 +52,7 @@ class CacheView:
     tables: Optional[torch.Tensor]  # [max_sequences, width] int32: this group's page ids, one row per slot
     block_size: int
     group: int
-    state: Optional[torch.Tensor]  # [max_sequences, ...] this cache's per-request state
+    state: object  # [max_sequences, ...] this cache's per-request state, or {name: tensor} of several
     slots: Optional[torch.Tensor]  # [requests in the step] int32 slot of each request (a row's is step.seq_of_row)
 
 
@@ -72,31 +72,45 @@ class DeviceCache:
         for gi, g in enumerate(groups):
             shape = (len(g.cache_ids), g.n_blocks, g.n_kv_heads, block_size, g.head_dim)
             self.k.append(torch.zeros(shape, dtype=runtime.dtype, device=runtime.device))
-            self.v.append(torch.zeros(shape, dtype=runtime.dtype, device=runtime.device))
+            vd = g.head_dim if g.v_head_dim is None else g.v_head_dim
+            self.v.append(torch.zeros(shape[:-1] + (vd,), dtype=runtime.dtype, device=runtime.device) if vd else None)
             for j, cid in enumerate(g.cache_ids):
                 self._where[cid] = (gi, j)
-        self.state = {}
+        def make(need):
+            return torch.zeros((max_sequences, *need.shape), dtype=_STATE_DTYPES[need.dtype], device=runtime.device)
+
+        self.state = {}  # cache number -> tensor, or {name: tensor} when the layer keeps several states
         for cid, needs in cache_needs.items():
-            if needs.state is not None:
-                self.state[cid] = torch.zeros((max_sequences, *needs.state.shape),
-                                              dtype=_STATE_DTYPES[needs.state.dtype], device=runtime.device)
+            if isinstance(needs.state, dict):
+                self.state[cid] = {name: make(need) for name, need in needs.state.items()}
+            elif needs.state is not None:
+                self.state[cid] = make(needs.state)
+
+    def _state_tensors(self):
+        for t in self.state.values():
+            yield from (t.values() if isinstance(t, dict) else (t,))
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v) + \
-            sum(t.numel() * t.element_size() for t in self.state.values())
+        return sum(t.numel() * t.element_size() for t in self.k + self.v if t is not None) + \
+            sum(t.numel() * t.element_size() for t in self._state_tensors())
 
     def bytes_per_token(self) -> int:
         """Key/value bytes one cached position occupies over all caches."""
-        return sum(2 * len(g.cache_ids) * g.n_kv_heads * g.head_dim * self.k[i].element_size()
+        return sum(len(g.cache_ids) * g.n_kv_heads * self.k[i].element_size()
+                   * (g.head_dim + (g.head_dim if g.v_head_dim is None else g.v_head_dim))
                    for i, g in enumerate(self.groups))
 
+    def state_bytes_per_request(self) -> int:
+        return sum(t[0].numel() * t.element_size() for t in self._state_tensors())
+
     def clear_slot(self, slot: int) -> None:
-        for t in self.state.values():
+        for t in self._state_tensors():
             t[slot].zero_()
 
     def view(self, cache_id: int, step) -> CacheView:
         gi, j = self._where.get(cache_id, (None, None))
         if gi is None:
             return CacheView(None, None, None, self.block_size, -1, self.state.get(cache_id), step.slots)
-        return CacheView(self.k[gi][j], self.v[gi][j], self.tables[gi], self.block_size, gi,
+        return CacheView(self.k[gi][j], self.v[gi][j] if self.v[gi] is not None else None, self.tables[gi],
+                         self.block_size, gi,
                          self.state.get(cache_id), step.slots)

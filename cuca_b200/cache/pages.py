@@ -44,6 +44,7 @@ class GroupLayout:
     window: Optional[int]
     cache_ids: tuple  # caches (run-order cache numbers) that live in this group
     n_blocks: int
+    v_head_dim: Optional[int] = None  # None: values as wide as keys; 0: the group has no value slab
 
 
 def _raise(code: int) -> None:

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to its model builder.
+"""One registry from an architecture's name (config.json `architectures[0]`, or `architecture`) to its model builder.
 
 A builder takes the parsed config.json and returns a `ModelSpec` (see
 `models/spec.py`). An unknown name is an error that lists the registered
@@ -28,13 +28,14 @@ def architectures() -> list[str]:
 
 
 def _ensure_builtin() -> None:
-    from ..models import llama  # noqa: F401  (registers itself)
+    from ..models import bananex, llama  # noqa: F401  (they register themselves)
 
 
 def build_spec(config_json: dict):
     """config.json (a dict) -> ModelSpec, through the registered builder of its architecture."""
     _ensure_builtin()
-    archs = config_json.get("architectures") or []
+    # Hugging Face folders list `architectures`; a file may also name its one `architecture`
+    archs = config_json.get("architectures") or ([config_json["architecture"]] if config_json.get("architecture") else [])
     if not archs:
         raise ConfigError("config.json is missing `architectures`")
     name = str(archs[0])

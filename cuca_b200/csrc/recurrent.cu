@@ -1,0 +1,259 @@
+// Recurrent mixers: state carried from token to token in 32-bit, one slot per request.
+//   mingru_scan        S = (1 - z) S + z c, gates from the current token alone
+//   causal_conv        short convolution per channel over a request's tokens, its last inputs kept per request
+//   ssm_scan           S = exp(-exp(A) dt) S + dt B x^T, y = S^T C + D x per head (scalar decay per head)
+//   gated_group_norm   y * silu(z), RMS-normed in equal parts, times a weight
+// A step brings each request a run of consecutive rows (req_row0, req_count); a kernel walks a request's rows in
+// order from the state its slot holds and leaves the new state there. The order of the arithmetic along a sequence
+// does not depend on where it was cut into steps.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float siluf_(float v) { return v / (1.f + expf(-v)); }
+
+// zxg: [rows, 3 W] 32-bit (z, u and g before their activations, biases added). One thread per (request, channel).
+template <typename TO>
+__global__ void mingru_scan_kernel(const float* __restrict__ zxg, float* __restrict__ state, TO* __restrict__ out,
+                                   const int* __restrict__ req_row0, const int* __restrict__ req_count,
+                                   const int* __restrict__ slots, int W) {
+  pdl_trigger();
+  pdl_wait();
+  const int q = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
+  if (slot < 0 || n <= 0 || c >= W) return;
+  float S = state[(size_t)slot * W + c];
+  for (int t = 0; t < n; ++t) {
+    const float* row = zxg + (size_t)(r0 + t) * 3 * W;
+    const float z = sigmoidf_(row[c]);
+    const float u = row[W + c];
+    const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+    S = (1.f - z) * S + z * cand;
+    out[(size_t)(r0 + t) * W + c] = from_f32<TO>(S * siluf_(row[2 * W + c]));
+  }
+  state[(size_t)slot * W + c] = S;
+}
+
+// in: 32-bit rows of stride ld_in, channel c at column col0 + c. kept: [slots, taps - 1, C] the inputs before the
+// request's first row of this step (zeros for a new request). Blocks y < n_rows take rows that have taps - 1 rows of
+// their own request before them in this step; blocks y >= n_rows take one request each: its first taps - 1 rows and
+// then its new kept inputs (only that block touches them).
+template <typename TW>
+__global__ void causal_conv_kernel(const float* __restrict__ in, int ld_in, int col0, const TW* __restrict__ w,
+                                   const TW* __restrict__ bias, float* __restrict__ kept, float* __restrict__ out,
+                                   const int* __restrict__ seq_of_row, const int* __restrict__ req_row0,
+                                   const int* __restrict__ req_count, const int* __restrict__ slots, int n_rows,
+                                   int C, int taps) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int b = blockIdx.y;
+  const int back = taps - 1;
+  const TW* wc = w + (size_t)c * taps;
+  const float b0 = bias ? to_f32(bias[c]) : 0.f;
+  if (b < n_rows) {
+    const int seq = seq_of_row[b];
+    if (seq < 0 || b < back || (back > 0 && seq_of_row[b - back] != seq)) return;
+    float acc = b0;
+    for (int k = 0; k < taps; ++k)
+      acc = fmaf(to_f32(wc[k]), in[(size_t)(b - back + k) * ld_in + col0 + c], acc);
+    out[(size_t)b * C + c] = siluf_(acc);
+    return;
+  }
+  if (back == 0) return;  // a one-tap convolution keeps nothing and every row was a plain row
+  const int q = b - n_rows;
+  const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
+  if (slot < 0 || n <= 0) return;
+  float* keep = kept + (size_t)slot * back * C;
+  // val(m): the input m rows after the request's first row of this step; m < 0 reaches into the kept inputs
+  auto val = [&](int m) -> float {
+    return m < 0 ? keep[(size_t)(m + back) * C + c] : in[(size_t)(r0 + m) * ld_in + col0 + c];
+  };
+  const int head = n < back ? n : back;
+  for (int j = 0; j < head; ++j) {
+    float acc = b0;
+    for (int k = 0; k < taps; ++k) acc = fmaf(to_f32(wc[k]), val(j - back + k), acc);
+    out[(size_t)(r0 + j) * C + c] = siluf_(acc);
+  }
+  // new kept inputs: the last `back` inputs of the sequence so far. Ascending k reads entries at or after the one
+  // it writes (old entry n + k for the new entry k), so nothing is overwritten before it is read.
+  for (int k = 0; k < back; ++k) {
+    const float v = val(n - back + k);
+    keep[(size_t)k * C + c] = v;
+  }
+}
+
+constexpr int SSM_MAXR = 32;  // state values a thread holds
+
+// One block per (head, request). Thread (p, s): value column p, state rows s * nr .. s * nr + nr - 1. state:
+// [slots, H, P, N]. xbc: 32-bit [rows, H P + 2 G N] after the convolution (x | B | C); dt_raw: rows of stride ld_dt,
+// head h at column dt_col + h, before bias and softplus.
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_raw, int ld_dt, int dt_col,
+                                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
+                                const int* __restrict__ req_row0, const int* __restrict__ req_count,
+                                const int* __restrict__ slots, int H, int P, int N, int G, int NS, int nr) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, q = blockIdx.y;
+  const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
+  if (slot < 0 || n <= 0) return;
+  const int p_raw = threadIdx.x / NS, s = threadIdx.x % NS;
+  const bool live = p_raw < P;
+  const int p = live ? p_raw : P - 1;
+  const int n0 = s * nr;
+  const int g = h / (H / G);
+  const int C = H * P + 2 * G * N;
+  float S[SSM_MAXR];
+  float* st = state + (((size_t)slot * H + h) * P + p) * N;
+#pragma unroll
+  for (int i = 0; i < SSM_MAXR; ++i) S[i] = (i < nr && n0 + i < N) ? st[n0 + i] : 0.f;
+  const float A = -expf(a_log[h]);
+  const float bias = dt_bias[h], D = d_skip[h];
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)(r0 + t);
+    const float v = dt_raw[row * ld_dt + dt_col + h] + bias;
+    const float dt = v > 20.f ? v : log1pf(expf(v));
+    const float decay = expf(A * dt);
+    const float* xr = xbc + row * C;
+    const float x = xr[h * P + p];
+    const float* Br = xr + H * P + g * N + n0;
+    const float* Cr = Br + G * N;
+    const float dx = dt * x;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < SSM_MAXR; ++i) {
+      if (i < nr && n0 + i < N) {
+        S[i] = fmaf(decay, S[i], dx * Br[i]);
+        acc = fmaf(S[i], Cr[i], acc);
+      }
+    }
+    for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (live && s == 0) y[row * (H * P) + h * P + p] = acc + D * x;
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < SSM_MAXR; ++i)
+      if (i < nr && n0 + i < N) st[n0 + i] = S[i];
+  }
+}
+
+// One block per (row, part). v = y * silu(z); out = v * rsqrt(mean over the part (v^2) + eps) * w.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ld_z, const TW* __restrict__ w,
+                        TO* __restrict__ out, int inner, int part, float eps) {
+  __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.y;
+  const int c0 = blockIdx.x * part;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < part; i += 256) {
+    const float v = y[row * inner + c0 + i] * siluf_(z[row * ld_z + c0 + i]);
+    s = fmaf(v, v, s);
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)part + eps);
+  for (int i = threadIdx.x; i < part; i += 256) {
+    const float v = y[row * inner + c0 + i] * siluf_(z[row * ld_z + c0 + i]);
+    out[row * inner + c0 + i] = from_f32<TO>(v * inv * to_f32(w[c0 + i]));
+  }
+}
+
+}  // namespace
+
+CUCA_API int cuca_mingru_scan(const float* zxg, float* state, void* out, int out_dtype, const int* req_row0,
+                              const int* req_count, const int* slots, int n_seqs, int W, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  CUCA_REQUIRE(W > 0 && n_seqs <= 65535, "mingru_scan: bad sizes W=%d requests=%d", W, n_seqs);
+  dim3 grid((W + 127) / 128, n_seqs);
+  if (out_dtype == CUCA_F32)
+    cuca_launch(mingru_scan_kernel<float>, grid, dim3(128), 0, stream, true, zxg, state, (float*)out, req_row0,
+                req_count, slots, W);
+  else if (out_dtype == CUCA_BF16)
+    cuca_launch(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, true, zxg, state, (__nv_bfloat16*)out,
+                req_row0, req_count, slots, W);
+  else
+    CUCA_REQUIRE(false, "mingru_scan: unknown dtype %d", out_dtype);
+  CUCA_CHECK_LAUNCH("mingru_scan");
+  return 0;
+}
+
+CUCA_API int cuca_causal_conv(const float* in, int ld_in, int col0, const void* w, const void* bias, int w_dtype,
+                              float* kept, float* out, const int* seq_of_row, const int* req_row0,
+                              const int* req_count, const int* slots, int n_rows, int n_seqs, int C, int taps,
+                              cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(C > 0 && taps >= 1, "causal_conv: bad sizes channels=%d taps=%d", C, taps);
+  CUCA_REQUIRE(n_rows + n_seqs <= 65535, "causal_conv: %d rows in one step exceed the launch limit", n_rows);
+  dim3 grid((C + 127) / 128, n_rows + n_seqs);
+  if (w_dtype == CUCA_F32)
+    cuca_launch(causal_conv_kernel<float>, grid, dim3(128), 0, stream, true, in, ld_in, col0, (const float*)w,
+                (const float*)bias, kept, out, seq_of_row, req_row0, req_count, slots, n_rows, C, taps);
+  else if (w_dtype == CUCA_BF16)
+    cuca_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, true, in, ld_in, col0,
+                (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, kept, out, seq_of_row, req_row0, req_count, slots,
+                n_rows, C, taps);
+  else
+    CUCA_REQUIRE(false, "causal_conv: unknown dtype %d", w_dtype);
+  CUCA_CHECK_LAUNCH("causal_conv");
+  return 0;
+}
+
+// How the state rows of a head are dealt to threads: (threads per value column, state rows per thread).
+CUCA_API int cuca_ssm_scan_split(int P, int N, int* ns_out, int* nr_out) {
+  int ns = 1;
+  while ((N + ns - 1) / ns > SSM_MAXR && ns < 32) ns <<= 1;
+  if ((N + ns - 1) / ns > SSM_MAXR) return 1;
+  while (ns < 32 && ns * 2 <= N && P * ns * 2 <= 256) ns <<= 1;
+  *ns_out = ns;
+  *nr_out = (N + ns - 1) / ns;
+  return 0;
+}
+
+CUCA_API int cuca_ssm_scan(const float* xbc, const float* dt_raw, int ld_dt, int dt_col, const float* dt_bias,
+                           const float* a_log, const float* d_skip, float* state, float* y, const int* req_row0,
+                           const int* req_count, const int* slots, int n_seqs, int H, int P, int N, int G,
+                           cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  CUCA_REQUIRE(H > 0 && P > 0 && N > 0 && G > 0 && H % G == 0, "ssm_scan: bad sizes heads=%d vdim=%d state=%d groups=%d",
+               H, P, N, G);
+  CUCA_REQUIRE(n_seqs <= 65535, "ssm_scan: %d requests exceed the launch limit", n_seqs);
+  int ns, nr;
+  CUCA_REQUIRE(cuca_ssm_scan_split(P, N, &ns, &nr) == 0, "ssm_scan: state size %d exceeds %d", N, 32 * SSM_MAXR);
+  const int threads = (P * ns + 31) / 32 * 32;
+  CUCA_REQUIRE(threads <= 1024, "ssm_scan: value size %d with %d threads per column exceeds a block", P, ns);
+  cuca_launch(ssm_scan_kernel, dim3(H, n_seqs), dim3(threads), 0, stream, true, xbc, dt_raw, ld_dt, dt_col, dt_bias,
+              a_log, d_skip, state, y, req_row0, req_count, slots, H, P, N, G, ns, nr);
+  CUCA_CHECK_LAUNCH("ssm_scan");
+  return 0;
+}
+
+CUCA_API int cuca_gated_group_norm(const float* y, const float* z, int ld_z, const void* w, int w_dtype, void* out,
+                                   int out_dtype, int n_rows, int inner, int parts, float eps, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(parts > 0 && inner % parts == 0, "gated_group_norm: %d parts do not divide %d", parts, inner);
+  CUCA_REQUIRE(n_rows <= 65535, "gated_group_norm: %d rows exceed the launch limit", n_rows);
+  dim3 grid(parts, n_rows);
+  const int part = inner / parts;
+#define GGN(TW, TO)                                                                                               \
+  cuca_launch(gated_group_norm_kernel<TW, TO>, grid, dim3(256), 0, stream, true, y, z, ld_z, (const TW*)w, (TO*)out, \
+              inner, part, eps)
+  if (w_dtype == CUCA_F32 && out_dtype == CUCA_F32) GGN(float, float);
+  else if (w_dtype == CUCA_BF16 && out_dtype == CUCA_BF16) GGN(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == CUCA_F32 && out_dtype == CUCA_BF16) GGN(float, __nv_bfloat16);
+  else CUCA_REQUIRE(false, "gated_group_norm: unsupported dtypes %d/%d", w_dtype, out_dtype);
+#undef GGN
+  CUCA_CHECK_LAUNCH("gated_group_norm");
+  return 0;
+}

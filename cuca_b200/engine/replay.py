@@ -21,10 +21,13 @@ import sys
 from pathlib import Path
 
 
+from ..config.model_config import read_config_json
+from ..config.registry import build_spec
+from ..weights.loader import FolderSource
 from .core import EngineCore
 from .step import StepEntry
 
-MAX_LIVE = 64
+MAX_LIVE = 4  # state slots: requests that are live at the same time
 
 
 class Replayer:
@@ -85,11 +88,15 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16, help="positions per page")
+    ap.add_argument("--max-live", type=int, default=MAX_LIVE, help="state slots: most requests live at the same time")
     args = ap.parse_args(argv)
     # --max-tokens counts every live request's tokens rounded up to 64; with larger pages each of those 64 may be a
     # request of its own that needs a whole page
     kv_tokens = -(-args.max_tokens // 64) * max(64, args.block_size)
-    core = EngineCore.from_folder(args.model, dtype=args.dtype, kv_tokens=kv_tokens, max_sequences=MAX_LIVE,
-                                  block_size=args.block_size, window_pools="full")
+    spec = build_spec(read_config_json(args.model))
+    # no request is longer than the pool; a model without a longest sequence of its own gets its tables that long
+    core = EngineCore(spec, FolderSource(args.model), dtype=args.dtype, kv_tokens=kv_tokens,
+                      context_length=min(spec.max_positions, kv_tokens), max_sequences=args.max_live,
+                      block_size=args.block_size, window_pools="full")
     Replayer(core, args.out).run(sys.stdin)
     return 0

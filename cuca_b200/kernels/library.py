@@ -67,6 +67,20 @@ _SIGNATURES = {
     "cuca_attention_plan": [_P, _P, _P, _I, _I, _P, _I, _P, _P, _I, _P],
     "cuca_random_normal": [_P, _I, c_size_t, c_size_t, ctypes.c_ulonglong, _F, _F, _P],
     "cuca_gemm_tc_supported": [_P, _P, _I, _I, _I, _I],
+    "cuca_norm_shift": [_P, _P, _I, _F, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "cuca_post_norm_add": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _F, _P],
+    "cuca_gelu": [_P, _I, c_size_t, _I, _P],
+    "cuca_scale": [_P, c_size_t, _F, _P],
+    "cuca_concat2": [_P, _P, _P, _I, _I, _I, _P],
+    "cuca_mingru_scan": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _P],
+    "cuca_causal_conv": [_P, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "cuca_ssm_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_gated_group_norm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _P],
+    "cuca_latent_max_rank": [],
+    "cuca_latent_prepare": [_P, _I, _I, _I, _I, _I, _P, _F, _P, _P, _I, _I, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I,
+                            _P, _P],
+    "cuca_head_linear": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_latent_attention": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }
 

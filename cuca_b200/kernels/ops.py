@@ -622,3 +622,113 @@ def rope_store_partial(partial: PartialSums, bias, q_out, positions, seq_of_row,
         _p(tables), tables.shape[1] if tables is not None else 0, _p(cos), _p(sin), table_rows, int(rotary_dim),
         _p(kpool), _p(vpool), n_blocks, int(block_size), q_out.shape[0], n_heads, n_kv_heads, head_dim, _p(err),
         _stream()), "rope_store_partial")
+
+
+# ------------------------------------------------------------------ blocks that norm a sublayer's input and output
+def _gain(g):
+    """(pointer, stride) of a norm's gain: a vector, or a single number for every coordinate."""
+    return _p(g), (0 if g.numel() == 1 else 1)
+
+
+def norm_shift(x, gain, eps, mix, kept, out, step) -> None:
+    """out[r] = h[r] + (h[r-1] - h[r]) * mix, h = RMSNorm(x) * gain; the row before a request's first row of the step
+    is `kept[slot]`, which then becomes the request's last h."""
+    _cuda(x, gain, mix, kept, out)
+    lib = library.load()
+    gp, gs = _gain(gain)
+    library.check(lib.cuca_norm_shift(_p(x), gp, gs, float(eps), _p(mix), _p(kept), _p(out), dtype_code(out.dtype),
+                                      _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots),
+                                      x.shape[0], step.n_seqs, x.shape[1], _stream()), "norm_shift")
+
+
+def post_norm_add(x, y, gain, eps, gain2=None, out=None) -> None:
+    """x += RMSNorm(y) * gain; with `out`: out = RMSNorm(new x) * gain2 in the same pass."""
+    _cuda(x, y, gain, out)
+    lib = library.load()
+    gp, gs = _gain(gain)
+    g2p, g2s = _gain(gain2) if out is not None else (None, 0)
+    library.check(lib.cuca_post_norm_add(_p(x), _p(y), gp, gs, g2p, g2s, _p(out),
+                                         dtype_code(out.dtype) if out is not None else 0, x.shape[0], x.shape[1],
+                                         float(eps), _stream()), "post_norm_add")
+
+
+def gelu_(a, tanh_form: bool = False) -> None:
+    _cuda(a)
+    library.check(library.load().cuca_gelu(_p(a), dtype_code(a.dtype), a.numel(), int(tanh_form), _stream()), "gelu")
+
+
+def scale_(a, s: float) -> None:
+    _cuda(a)
+    if a.dtype != torch.float32:
+        raise library.KernelError("scale_ takes a 32-bit tensor")
+    library.check(library.load().cuca_scale(_p(a), a.numel(), float(s), _stream()), "scale")
+
+
+def concat2(a, b, out) -> None:
+    """out[r] = [a[r] | b[r]] in out's dtype; a, b are 32-bit [rows, E]."""
+    _cuda(a, b, out)
+    library.check(library.load().cuca_concat2(_p(a), _p(b), _p(out), dtype_code(out.dtype), a.shape[0], a.shape[1],
+                                              _stream()), "concat2")
+
+
+# ------------------------------------------------------------------ recurrent mixers
+def mingru_scan(zxg, state, out, step) -> None:
+    _cuda(zxg, state, out)
+    library.check(library.load().cuca_mingru_scan(_p(zxg), _p(state), _p(out), dtype_code(out.dtype),
+                                                  _p(step.req_row0), _p(step.req_count), _p(step.slots), step.n_seqs,
+                                                  out.shape[1], _stream()), "mingru_scan")
+
+
+def causal_conv(src, col0, weight, bias, kept, out, step) -> None:
+    """out[r, c] = silu(bias[c] + sum_k weight[c, k] * src[r - (taps-1) + k, col0 + c]) along each request; inputs
+    before a request's first row of the step come from `kept[slot]` ([taps - 1, C]), which is brought up to date."""
+    _cuda(src, weight, kept, out)
+    C, taps = weight.shape
+    library.check(library.load().cuca_causal_conv(
+        _p(src), src.stride(0), int(col0), _p(weight), _p(bias), dtype_code(weight.dtype), _p(kept), _p(out),
+        _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots), src.shape[0], step.n_seqs, C, taps,
+        _stream()), "causal_conv")
+
+
+def ssm_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state, y, step, H, P, N, G) -> None:
+    _cuda(xbc, proj, state, y)
+    library.check(library.load().cuca_ssm_scan(
+        _p(xbc), _p(proj), proj.stride(0), int(dt_col), _p(dt_bias), _p(a_log), _p(d_skip), _p(state), _p(y),
+        _p(step.req_row0), _p(step.req_count), _p(step.slots), step.n_seqs, H, P, N, G, _stream()), "ssm_scan")
+
+
+def gated_group_norm(y, z, weight, out, parts, eps) -> None:
+    """out = RMSNorm over `parts` equal parts of (y * silu(z)) times weight; z: 32-bit rows of stride z.stride(0)."""
+    _cuda(y, z, weight, out)
+    library.check(library.load().cuca_gated_group_norm(
+        _p(y), _p(z), z.stride(0), _p(weight), dtype_code(weight.dtype), _p(out), dtype_code(out.dtype), y.shape[0],
+        y.shape[1], int(parts), float(eps), _stream()), "gated_group_norm")
+
+
+# ------------------------------------------------------------------ attention over a cached latent
+LATENT_MAX_RANK = 1024  # `cuca_latent_max_rank` says the same
+
+
+def latent_prepare(qkg, H, dn, dr, rank, c_gain, eps, cos, sin, rot_dims, qk, cache, step, err) -> None:
+    lib = library.load()
+    pool = cache.k
+    library.check(lib.cuca_latent_prepare(
+        _p(qkg), qkg.stride(0), H, dn, dr, rank, _p(c_gain), float(eps), _p(cos), _p(sin), cos.shape[0], int(rot_dims),
+        _p(qk), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
+        _p(cache.tables), cache.tables.shape[1], qkg.shape[0], _p(err), _stream()), "latent_prepare")
+
+
+def head_linear(a, lda, a_head, w, out, ldo, o_head, T, gate=None, ldg=0) -> None:
+    """out[t, h, :] = w[h] @ a[t, h, :] for every head (w: [H, N, K]; a 32-bit), optionally times sigmoid(gate)."""
+    H, N, K = w.shape
+    library.check(library.load().cuca_head_linear(
+        _p(a), int(lda), int(a_head), _p(w), dtype_code(w.dtype), _p(out), dtype_code(out.dtype), int(ldo), int(o_head),
+        _p(gate), int(ldg), int(T), H, N, K, _stream()), "head_linear")
+
+
+def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> None:
+    pool = cache.k
+    library.check(library.load().cuca_latent_attention(
+        _p(qk), _p(out), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions),
+        _p(step.seq_of_row), _p(cache.tables), cache.tables.shape[1], qk.shape[0], H, rank, Dk, float(scale),
+        int(window or 0), _p(err), _stream()), "latent_attention")

@@ -3,11 +3,12 @@ from __future__ import annotations
 
 import torch
 
-from ..parts import attention, block, embedding, mlp, norm, rope  # noqa: F401  (register the built-in parts)
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TensorNeed
+from ..parts import (attention, block, embedding, latent_attention, mlp, norm, recurrent, rope,  # noqa: F401
+                     stream_ops)  # (register the built-in parts)
+from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, STREAM_OPS, TensorNeed
 from ..parts.embedding import OutputHead, TokenEmbedding
 from ..weights import loader
-from .spec import ModelSpec
+from .spec import Between, ModelSpec
 
 
 class Model:
@@ -26,6 +27,7 @@ class Model:
             mixer_norm = NORMS.get(ls.mixer_norm.kind)(ls.mixer_norm, runtime) if ls.mixer_norm else None
             ffn_norm = NORMS.get(ls.ffn_norm.kind)(ls.ffn_norm, runtime) if ls.ffn_norm else None
             self.blocks.append(BLOCKS.get(ls.block.kind)(ls.block, runtime, mixer, ffn, mixer_norm, ffn_norm))
+        self.stream_ops = [STREAM_OPS.get(s.kind)(s, runtime) for s in spec.stream_ops]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, runtime)
         self.head = OutputHead(spec.head, runtime)
         self.loaded = False
@@ -35,6 +37,7 @@ class Model:
         yield self.embedding
         for b in self.blocks:
             yield from b.parts()
+        yield from self.stream_ops
         yield self.final_norm
         yield self.head
 
@@ -50,13 +53,13 @@ class Model:
     def cache_needs(self) -> dict:
         """cache number -> what its owning layer's mixer keeps there."""
         out = {}
-        for run in self.spec.schedule:
+        for run in self.spec.runs():
             if run.owns:
-                out[run.cache] = self.blocks[run.layer].mixer.cache_needs()
+                out[run.cache] = self.blocks[run.layer].cache_needs()
         return out
 
     def graph_safe(self) -> bool:
-        return all(b.mixer.graph_safe and (b.feed_forward is None or b.feed_forward.graph_safe) for b in self.blocks)
+        return all(b.graph_safe for b in self.blocks)
 
     # ------------------------------------------------------------ weights
     def check_weights(self, source: loader.WeightSource) -> None:
@@ -87,7 +90,10 @@ class Model:
         """Bytes of weights one step reads (every layer's parts once per run, the head, no embedding table)."""
         total = self.final_norm.weight_bytes() + self.head.weight_bytes()
         for run in self.spec.schedule:
-            total += sum(p.weight_bytes() for p in self.blocks[run.layer].parts())
+            if isinstance(run, Between):
+                total += self.stream_ops[run.op].weight_bytes()
+            else:
+                total += sum(p.weight_bytes() for p in self.blocks[run.layer].parts())
         return total
 
     # ------------------------------------------------------------ step
@@ -96,8 +102,15 @@ class Model:
         x = torch.empty(step.n_rows, self.spec.width, dtype=torch.float32, device=self.rt.device)
         self.embedding.forward(step.tokens, x)
         stream = self.rt.stream(x)
+        origin = None
+        if self.stream_ops:  # they read the embedding output, which the layers overwrite in place
+            origin = torch.empty_like(x)
+            self.embedding.forward(step.tokens, origin)
         for run in self.spec.schedule:
-            self.blocks[run.layer].forward(stream, step, cache.view(run.cache, step))
+            if isinstance(run, Between):
+                self.stream_ops[run.op].forward(stream, origin, step, run.arg)
+            else:
+                self.blocks[run.layer].forward(stream, step, cache.view(run.cache, step))
         if step.logit_rows is None or step.n_logit_rows == 0:
             stream.drop_pending()
             return None

@@ -33,6 +33,15 @@ class Run:
     owns: bool = True
 
 
+@dataclass(frozen=True)
+class Between:
+    """A run-order entry that is no layer: stream operation `op` (an index into `ModelSpec.stream_ops`) happens to
+    the residual stream at this point, with `arg` telling it which of its occasions this is (the pass of a loop)."""
+
+    op: int
+    arg: int = 0
+
+
 @dataclass
 class ModelSpec:
     architecture: str
@@ -46,10 +55,20 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: tuple = ()
     ignorable_tensor: Callable[[str], bool] = field(default=lambda name: False)
+    stream_ops: list = field(default_factory=list)  # PartSpecs of what `Between` entries of the schedule name
+
+    def runs(self):
+        """The schedule's layer runs, without what happens between them."""
+        return [e for e in self.schedule if isinstance(e, Run)]
 
     def validate(self) -> None:
         owners = {}
         for i, run in enumerate(self.schedule):
+            if isinstance(run, Between):
+                if not 0 <= run.op < len(self.stream_ops):
+                    raise ValueError(f"run order entry {i} names stream operation {run.op}; the model has "
+                                     f"{len(self.stream_ops)}")
+                continue
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run order entry {i} names layer {run.layer}; the model has {len(self.layers)}")
             if run.owns:

@@ -54,6 +54,7 @@ class KvNeeds:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: all keys; w: the last w keys
+    v_head_dim: Optional[int] = None  # None: values as wide as keys; 0: no value slab (the mixer reads values out of its key rows)
 
 
 @dataclass(frozen=True)
@@ -66,8 +67,11 @@ class StateNeeds:
 
 @dataclass
 class CacheNeeds:
+    """`state` is one `StateNeeds` or several by name (`{name: StateNeeds}`); the cache view hands back a tensor
+    `[max_sequences, ...]` or a dict of them accordingly."""
+
     kv: Optional[KvNeeds] = None
-    state: Optional[StateNeeds] = None
+    state: Any = None
 
 
 class Part:
@@ -124,6 +128,16 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamOp(Part):
+    """Something that happens to the whole residual stream between layers (a run-order entry of its own): it may
+    rewrite the stream from itself and from the embedding output. `forward(stream, origin, step, arg)`: `stream` is
+    the `ResidualStream`, `origin` the 32-bit embedding output of the step's rows (never written), `arg` the
+    run-order entry's number (which pass of a loop this is, for instance)."""
+
+    def forward(self, stream, origin, step, arg: int) -> None:  # pragma: no cover - interface
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of norms, mixer and feed-forward around the residual stream."""
 
@@ -136,7 +150,16 @@ class Block(Part):
         self.ffn_norm = ffn_norm
 
     def parts(self):
-        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None] + [self]
+
+    def cache_needs(self) -> CacheNeeds:
+        """What one run of this layer keeps per request: its mixer's needs, plus whatever the arrangement itself
+        carries from token to token."""
+        return self.mixer.cache_needs()
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.mixer.graph_safe and (self.feed_forward is None or self.feed_forward.graph_safe)
 
     def forward(self, stream, step, cache) -> None:  # pragma: no cover - interface
         raise NotImplementedError
@@ -172,12 +195,14 @@ class Registry:
 
 
 NORMS = Registry("norm")
+STREAM_OPS = Registry("stream operation")
 POSITIONS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block arrangement")
 
 register_norm = NORMS.register
+register_stream_op = STREAM_OPS.register
 register_position = POSITIONS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register

@@ -32,12 +32,14 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
-    """params: vocab, width. tensors: weight [vocab, width] (the embedding's name when tied)."""
+    """params: vocab, width, scale (a factor on the logits, default 1). tensors: weight [vocab, width] (the
+    embedding's name when tied)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def tensors(self):
@@ -50,4 +52,7 @@ class OutputHead(Part):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, h) -> torch.Tensor:
-        return self.rt.linear(h, self.weight, out_dtype=torch.float32)
+        logits = self.rt.linear(h, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
+        return logits

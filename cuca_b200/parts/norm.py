@@ -14,13 +14,14 @@ class RMSNorm(Norm):
         super().__init__(spec, runtime)
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
-        self.weight = None
+        self.weight = self.gain = None
 
     def tensors(self):
         return {self.spec.tensors["weight"]: TensorNeed((self.width,), keep_fp32=True, init="ones")}
 
     def load(self, get):
         self.weight = get(self.spec.tensors["weight"])
+        self.gain = self.weight  # what kernels that take "a gain" get: the vector
 
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
@@ -35,3 +36,21 @@ class RMSNorm(Norm):
         else:
             ops.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """RMSNorm whose gain is one number for every coordinate: h = x * rsqrt(mean(x^2) + eps) * g.
+    params: width, eps. tensors: weight [] (a single number). `gain` is that number as a 32-bit tensor of one
+    element (kernels that take a gain take it with stride 0); `weight` is it spread over the width for the kernels
+    that want a vector."""
+
+    def tensors(self):
+        return {self.spec.tensors["weight"]: TensorNeed((), keep_fp32=True, init="ones")}
+
+    def load(self, get):
+        self.gain = get(self.spec.tensors["weight"]).reshape(1).contiguous()
+        self.weight = self.gain.expand(self.width).contiguous()
+
+    def weight_bytes(self):
+        return self.gain.element_size()

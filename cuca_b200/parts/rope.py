@@ -49,7 +49,7 @@ def rope_tables(positions: int, n_dims: int, base: float, factors=None, freq_sca
 
 @register_position("rope")
 class RotaryEncoding(PositionEncoding):
-    """params: head_dim, rotary_dim, theta, scaling {kind, factor, low_freq_factor, high_freq_factor,
+    """params: head_dim, rotary_dim, theta, pairs ("half" | "adjacent"), scaling {kind, factor, low_freq_factor, high_freq_factor,
     original_max_position_embeddings}."""
 
     def __init__(self, spec, runtime):
@@ -59,6 +59,11 @@ class RotaryEncoding(PositionEncoding):
         self.rotary_dim = int(p.get("rotary_dim", self.head_dim))
         self.theta = float(p["theta"])
         self.scaling = dict(p.get("scaling") or {"kind": "default"})
+        # which dimensions turn together: "half" pairs i with i + n/2, "adjacent" pairs 2i with 2i + 1. The tables
+        # are the same; the kernel that applies them must pair as the model does
+        self.pairs = str(p.get("pairs", "half"))
+        if self.pairs not in ("half", "adjacent"):
+            raise ValueError(f"rotary pairs `{self.pairs}` are unknown; known: half, adjacent")
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary size {self.rotary_dim} must be even and at most the head size {self.head_dim}")
         self.cos = self.sin = None
@@ -82,4 +87,6 @@ class RotaryEncoding(PositionEncoding):
         self.sin = sin.to(self.rt.device)
 
     def fused_tables(self):
+        if self.pairs != "half":
+            raise ValueError("the fused rotate-and-store kernel pairs dimension i with i + n/2")
         return self.cos, self.sin, self.rotary_dim

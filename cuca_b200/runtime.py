@@ -80,6 +80,22 @@ class ResidualStream:
         self.rt = runtime
         self._tensor = tensor
         self._pending = None
+        self._unwritten = False
+
+    @classmethod
+    def unwritten(cls, runtime: "Runtime", rows: int, width: int) -> "ResidualStream":
+        """A stream that holds nothing yet (a sublayer's output gathered apart from the model's stream, for a norm
+        on it): the first contraction added to it is stored instead, so it needs no zeroing."""
+        s = cls(runtime, torch.empty(rows, width, dtype=torch.float32, device=runtime.device))
+        s._unwritten = True
+        return s
+
+    def replace(self, tensor: torch.Tensor) -> None:
+        """The stream is `tensor` from now on (an operation that rewrote the whole stream out of place)."""
+        if tensor.dtype != torch.float32 or tensor.shape != self._tensor.shape:
+            raise ValueError("a residual stream is replaced by a 32-bit tensor of its own shape")
+        self._pending = None
+        self._tensor = tensor
 
     @property
     def shape(self):
@@ -88,6 +104,9 @@ class ResidualStream:
     @property
     def data(self) -> torch.Tensor:
         """The stream's tensor with everything added; it may be read and updated in place."""
+        if self._unwritten:
+            self._tensor.zero_()
+            self._unwritten = False
         if self._pending is not None:
             ps, self._pending = self._pending, None
             ops.add_partials(self._tensor, ps)
@@ -96,12 +115,19 @@ class ResidualStream:
     def take(self):
         """(tensor, pending slices or None) for a reader that adds the slices itself, in the stream too: after
         the reader's kernel the tensor must hold the sum."""
+        if self._unwritten:
+            self._tensor.zero_()
+            self._unwritten = False
         ps, self._pending = self._pending, None
         return self._tensor, ps
 
     def add_linear(self, a, w, bias=None) -> None:
         """stream += a @ w.T (+ bias). Over few tokens the slices may stay pending until the next reader."""
         rt = self.rt
+        if self._unwritten:
+            self._unwritten = False
+            ops.gemm(a, w, self._tensor, ops.EPI_STORE, bias, rt.err)
+            return
         if rt.use_partials and bias is None and ops.gemm_partial_supported(a, w):
             x = self.data  # slices of an earlier contraction go in first
             self._pending = ops.gemm_partial(a, w, rt.err)
