@@ -192,6 +192,120 @@ def contraction_table(args, token_counts) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design bananex: the Bananex decoder beside a Llama of equal width, feed-forward size and layer count
+def _bananex_config(width, ff, heads, layers, vocab, window):
+    """`layers` layers in turn latent attention, minGRU, Mamba-2 (sizes in the proportions of published models of
+    each kind: latent 4 x head size, value columns of 64 with a state of 128), the first half of them looped twice."""
+    d = width // heads
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d,
+                        "mask": {"size": window}, "rot": {"base": 10000.0, "dims": d // 2},
+                        "scale": (d + d // 2) ** -0.5}}
+    gru = {"type": "mingru", "mlp": {"kind": "dense", "ff": ff}, "mixer": {"width": width}}
+    ssm = {"type": "mamba2", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    kinds = [latent, gru, ssm]
+    return {"architecture": "Bananex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [kinds[i % 3] for i in range(layers)], "loop": {"start": 0, "stop": layers // 2, "times": 2}}
+
+
+def _llama_config(width, ff, heads, layers, vocab):
+    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
+            "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
+            "head_dim": width // heads, "intermediate_size": ff, "vocab_size": vocab,
+            "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "rope_scaling": None,
+            "tie_word_embeddings": False}
+
+
+DESIGN_SIZES = {  # name -> (width, feed-forward, heads, layers, vocabulary)
+    "1b": (2048, 8192, 16, 6, 32000), "3b": (3072, 8192, 24, 6, 32000), "8b": (4096, 14336, 32, 6, 32000)}
+
+
+def design_table(args) -> int:
+    """Prefill of one prompt and decode steps of `--batch` requests for the Bananex decoder and for a Llama of the
+    same width, feed-forward size and number of layer runs, one JSON line per size and model: tokens/s of both
+    phases, the decode step's bytes (weights once, what a request keeps) over the measured copy bandwidth."""
+    import numpy as np
+    import torch
+
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig, RandomWeights
+    from cuca_b200.engine.scheduler import DECODE, Request
+    from cuca_b200.kernels import library
+
+    pk = peaks()
+    T, P, B = args.prefill_tokens or 2048, args.prompt_tokens or 1024, args.batch
+    steps, warmup = min(args.steps, 64), args.warmup
+    ctx = max(T, P + steps + warmup + 64) + 64
+    for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
+        width, ff, heads, layers, vocab = DESIGN_SIZES[size]
+        runs = layers + layers // 2  # the looped half runs twice
+        for name, cfg in (("bananex", _bananex_config(width, ff, heads, layers, vocab, window=1024)),
+                          ("llama", _llama_config(width, ff, heads, runs, vocab))):
+            model = LocalModel.load(LocalModelConfig(
+                model_config=cfg, random_weights=RandomWeights(seed=3, std=0.02), dtype="bfloat16", context_length=ctx,
+                kv_block_size=16, batching=BatchingConfig(max_sequences=B, kv_tokens=B * (ctx + 64) + 2048,
+                                                          max_step_tokens=max(2048, B), prefill_chunk=2048)))
+            core, sched, backend = model.core, model.scheduler, model.backend
+            rng = np.random.default_rng(1)
+            new_prompt = lambda n: rng.integers(0, vocab, size=n).tolist()  # noqa: E731
+
+            def timed(fn):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                out = fn()
+                b.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b), out
+
+            for _ in range(3):
+                model.generate(new_prompt(T), max_tokens=1, temperature=0.0)
+            prefill_ms = statistics.median(timed(lambda: model.generate(new_prompt(T), max_tokens=1,
+                                                                        temperature=0.0))[0] for _ in range(5))
+            seqs = [sched.submit(Request(new_prompt(P), max_tokens=steps + warmup + 64, temperature=0.0))
+                    for _ in range(B)]
+            for _ in range(8 * B + 16):
+                if all(s.phase == DECODE for s in seqs) or sched.turn() == 0:
+                    break
+            if not all(s.phase == DECODE for s in seqs):
+                raise RuntimeError("bench: the prompts did not all reach the decode phase")
+            torch.cuda.synchronize()
+            time.sleep(SETTLE_S)
+            hist = backend.burst(seqs, [s.pending for s in seqs], warmup)
+            launches0 = library.launches
+            ms, hist = timed(lambda: backend.burst(seqs, hist[-1].tolist(), steps, check=False))
+            core.rt.check_device_errors()
+            g = backend.graphs.get(B, seqs[0].blocks.length, False)
+            mean_ctx = seqs[0].blocks.length - steps / 2.0
+            for s in list(seqs):
+                sched.cancel(s)
+            sched.finished.clear()
+            # a windowed cache is read up to its window; state is read and written once per step
+            per_request = 0
+            for gi, grp in enumerate(core.groups):
+                seen = mean_ctx if grp.window is None else min(mean_ctx, grp.window)
+                vd = grp.head_dim if grp.v_head_dim is None else grp.v_head_dim
+                per_request += seen * len(grp.cache_ids) * grp.n_kv_heads * (grp.head_dim + vd) * 2
+            per_request += 2 * core.cache.state_bytes_per_request()
+            step_bytes = core.model.weight_bytes() + B * per_request
+            ms_step = ms / steps
+            print(json.dumps({
+                "design": name, "size": size, "width": width, "ff": ff, "heads": heads, "layer_runs": runs,
+                "vocab": vocab, "dtype": "bf16", "prefill_tokens": T, "prefill_ms": round(prefill_ms, 3),
+                "prefill_tokens_per_s": round(T / (prefill_ms / 1e3), 1), "decode_batch": B, "decode_prompt": P,
+                "decode_ms_per_step": round(ms_step, 4), "decode_tokens_per_s": round(B / (ms_step / 1e3), 1),
+                "decode_bytes_per_step": int(step_bytes),
+                "decode_frac_of_copy_bandwidth": round(step_bytes / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                "launches_per_decode_step": getattr(g, "launches", 0), "peaks": pk["source"],
+                "graphs": bool(backend.use_graphs)}), flush=True)
+            del model, core, sched, backend, seqs, g
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -211,6 +325,10 @@ def main() -> int:
                          "library's kernels beside cuBLAS (torch.matmul), cold weights; one JSON line per count")
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
+    ap.add_argument("--design", default=None, choices=["bananex"],
+                    help="instead of the bench: prefill and decode of this design beside a Llama of equal width, "
+                         "feed-forward size and layer runs, at --sizes (1b,3b,8b layer sizes; a few layers each)")
+    ap.add_argument("--sizes", default=None, help="with --design: which of 1b,3b,8b (all else)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -232,6 +350,8 @@ def main() -> int:
 
     if args.contractions:
         return contraction_table(args, [int(m) for m in args.contractions.split(",")])
+    if args.design:
+        return design_table(args)
 
     from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig, RandomWeights
     from cuca_b200.engine.scheduler import DECODE, Request

@@ -25,6 +25,11 @@ __device__ __forceinline__ float row_sumsq(const float* __restrict__ xr, int E, 
   return tot;
 }
 
+// A normed value and the shift, rounded step by step: the previous token's value is the same bits whether it is
+// computed here from its row or read back from where an earlier step kept it (no contraction across the two).
+__device__ __forceinline__ float normed(float x, float inv, float g) { return __fmul_rn(__fmul_rn(x, inv), g); }
+__device__ __forceinline__ float shifted(float h, float hp, float mix) { return __fmaf_rn(__fsub_rn(hp, h), mix, h); }
+
 // Blocks 0..n_rows-1 take the rows that follow another row of their request in this step; blocks n_rows.. take one
 // request each: its first row (whose predecessor is the request's kept row) and, after that, the new kept row.
 // Only that block touches the request's kept row, reading before it writes.
@@ -47,8 +52,7 @@ norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ gain, i
     const float ip = rsqrtf(row_sumsq(xp, E, red) / (float)E + eps);
     for (int i = threadIdx.x; i < E; i += NT) {
       const float g = gain[i * gain_stride];
-      const float h = xr[i] * ir * g, hp = xp[i] * ip * g;
-      out[(size_t)b * E + i] = from_f32<TO>(h + (hp - h) * mix[i]);
+      out[(size_t)b * E + i] = from_f32<TO>(shifted(normed(xr[i], ir, g), normed(xp[i], ip, g), mix[i]));
     }
     return;
   }
@@ -62,9 +66,8 @@ norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ gain, i
   const float il = rsqrtf(row_sumsq(xl, E, red) / (float)E + eps);
   for (int i = threadIdx.x; i < E; i += NT) {
     const float g = gain[i * gain_stride];
-    const float h = xr[i] * ir * g, hp = keep[i];
-    out[(size_t)r0 * E + i] = from_f32<TO>(h + (hp - h) * mix[i]);
-    keep[i] = xl[i] * il * g;
+    out[(size_t)r0 * E + i] = from_f32<TO>(shifted(normed(xr[i], ir, g), keep[i], mix[i]));
+    keep[i] = normed(xl[i], il, g);
   }
 }
 

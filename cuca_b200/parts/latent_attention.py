@@ -17,6 +17,7 @@ import math
 import torch
 
 from ..kernels import ops
+from . import rope  # noqa: F401  (registers the rotary tables this mixer asks for)
 from .base import POSITIONS, CacheNeeds, KvNeeds, Mixer, PartSpec, TensorNeed, register_mixer
 
 

@@ -17,6 +17,14 @@ import math
 import numpy as np
 
 
+ROUND = None  # a function that rounds an array to the engine's 16-bit format, or None: exact
+
+
+def mm(a, W):
+    """a W^T; with `ROUND` set, `a` is rounded first, as a 16-bit engine rounds what enters a contraction."""
+    return (ROUND(a) if ROUND is not None else a) @ W.T
+
+
 def rms(v, eps):
     return v / np.sqrt(np.mean(v * v, axis=-1, keepdims=True) + eps)
 
@@ -60,13 +68,18 @@ def latent_attention(h, w, p, m, eps):
     """Keys and values come from a low-rank latent; one rotated key part is shared by the heads."""
     T = h.shape[0]
     H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    win = m["mask"]["size"]
+    win = m["mask"]["size"] if m.get("mask") else T  # no mask: every earlier key
     pos = np.arange(T)
-    q = (h @ w[p + "q"].T).reshape(T, H, dn + dr)
-    q_plain, q_rot = q[..., :dn], rotate_adjacent(q[..., dn:], pos, m["rot"]["base"], m["rot"]["dims"])
-    dkv = h @ w[p + "dkv"].T
+    q = mm(h, w[p + "q"]).reshape(T, H, dn + dr)
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}
+    q_plain, q_rot = q[..., :dn], rotate_adjacent(q[..., dn:], pos, rot["base"], rot["dims"])
+    dkv = mm(h, w[p + "dkv"])
     c = rms(dkv[:, :r], eps) * w[p + "dkv.norm"]
-    k_rot = rotate_adjacent(dkv[:, r:], pos, m["rot"]["base"], m["rot"]["dims"])  # [T, dr], every head's
+    if ROUND is not None:  # the cache holds 16-bit values
+        c = ROUND(c)
+    k_rot = rotate_adjacent(dkv[:, r:], pos, rot["base"], rot["dims"])  # [T, dr], every head's
+    if ROUND is not None:
+        k_rot = ROUND(k_rot)
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, dn)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     out = np.zeros((T, H, dv))
@@ -77,21 +90,21 @@ def latent_attention(h, w, p, m, eps):
                           for j in range(lo, i + 1)])
             e = np.exp(s - s.max())
             out[i, a] = (e / e.sum()) @ v[lo:i + 1, a]
-    gate = sigmoid(h @ w[p + "g"].T)
-    return (out.reshape(T, H * dv) * gate) @ w[p + "o"].T
+    gate = sigmoid(mm(h, w[p + "g"]))
+    return mm(out.reshape(T, H * dv) * gate, w[p + "o"])
 
 
 def mingru(h, w, p, m):
     """S_t = (1 - z_t) S_(t-1) + z_t c_t, gates from the current token alone."""
-    z = sigmoid(h @ w[p + "z"].T + w[p + "z.b"])
-    u = h @ w[p + "x"].T + w[p + "x.b"]
+    z = sigmoid(mm(h, w[p + "z"]) + w[p + "z.b"])
+    u = mm(h, w[p + "x"]) + w[p + "x.b"]
     cand = np.where(u >= 0, u + 0.5, sigmoid(u))
     S = np.zeros(m["width"])
     states = np.zeros_like(z)
     for t in range(h.shape[0]):
         S = (1.0 - z[t]) * S + z[t] * cand[t]
         states[t] = S
-    return (states * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return mm(states * silu(mm(h, w[p + "g"])), w[p + "o"])
 
 
 def mamba2(h, w, p, m, eps):
@@ -99,7 +112,7 @@ def mamba2(h, w, p, m, eps):
     T = h.shape[0]
     H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
     inner = H * P
-    proj = h @ w[p + "in"].T
+    proj = mm(h, w[p + "in"])
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
     padded = np.concatenate([np.zeros((taps - 1, xbc.shape[1])), xbc], axis=0)
     conv = np.zeros_like(xbc)
@@ -121,11 +134,11 @@ def mamba2(h, w, p, m, eps):
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[p + "norm"]
-    return y @ w[p + "o"].T
+    return mm(y, w[p + "o"])
 
 
 def dense_ff(h, w, p):
-    return gelu_erf(h @ w[p + "up"].T + w[p + "up.b"]) @ w[p + "down"].T + w[p + "down.b"]
+    return mm(gelu_erf(mm(h, w[p + "up"]) + w[p + "up.b"]), w[p + "down"]) + w[p + "down.b"]
 
 
 def layer(x, w, i, spec, eps):
@@ -166,8 +179,8 @@ def forward(cfg, w, tokens, trace=None):
     e = x.copy()
     for i, t, first in run_order(cfg):
         if first:
-            x = np.concatenate([x, e], axis=1) @ w["loop.in"].T + w["loop.step"][t]
+            x = mm(np.concatenate([x, e], axis=1), w["loop.in"]) + w["loop.step"][t]
         x = layer(x, w, i, cfg["layers"][i], eps)
         if trace is not None:
             trace.append(x.copy())
-    return (rms(x, eps) * w["final.norm"]) @ w["head"].T * cfg["logit_scale"]
+    return mm(rms(x, eps) * w["final.norm"], w["head"]) * cfg["logit_scale"]

@@ -104,14 +104,20 @@ def peak_tokens(steps: list) -> int:
 
 
 # ---------------------------------------------------------------- running
-def run_in_process(model_dir, dtype: str, steps: list, max_tokens: int, block_size: int = 16) -> dict:
+def run_in_process(model_dir, dtype: str, steps: list, max_tokens: int, block_size: int = 16,
+                   window_pools: str = "full") -> dict:
     """Replay through the framework's Replayer in this process; returns step -> logits [wanted, vocab]."""
+    from cuca_b200.config.model_config import read_config_json
+    from cuca_b200.config.registry import build_spec
     from cuca_b200.engine.core import EngineCore
     from cuca_b200.engine.replay import MAX_LIVE, Replayer
 
     out = tempfile.mkdtemp(prefix="replay_out_")
+    # a model that names no longest sequence gets position tables as long as the pool
+    longest = build_spec(read_config_json(model_dir)).max_positions
     core = EngineCore.from_folder(model_dir, dtype=dtype, kv_tokens=round64(max_tokens), max_sequences=MAX_LIVE,
-                                  block_size=block_size, window_pools="full")
+                                  context_length=min(longest, max(round64(max_tokens), 64)),
+                                  block_size=block_size, window_pools=window_pools)
     rp = Replayer(core, out)
     with open(os.devnull, "w") as sink:
         rp.run([json.dumps(s) for s in steps], echo=sink)
@@ -131,7 +137,8 @@ def run_subprocess(model_dir, dtype: str, steps: list, max_tokens: int, env=None
     assert r.returncode == 0, f"trace_run failed:\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
     done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps]
-    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    cfg = json.loads((Path(model_dir) / "config.json").read_text())
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     return read_outputs(out, steps, vocab)
 
 
