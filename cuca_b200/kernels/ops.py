@@ -726,8 +726,38 @@ def head_linear(a, lda, a_head, w, out, ldo, o_head, T, gate=None, ldg=0) -> Non
         _p(gate), int(ldg), int(T), H, N, K, _stream()), "head_linear")
 
 
+USE_MMA_LATENT = True  # bfloat16 caches through the tensor-core form where the sizes allow
+LATENT_TILE_ROWS = 16  # tokens of a portion that one CTA of the tensor-core form takes
+_latent_mma_ok: dict = {}
+
+
+def latent_attention_mma_supported(rank: int, Dk: int) -> bool:
+    key = (rank, Dk)
+    if key not in _latent_mma_ok:
+        _latent_mma_ok[key] = bool(library.load().cuca_latent_attention_mma_supported(rank, Dk))
+    return _latent_mma_ok[key]
+
+
 def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> None:
+    """Every row's heads attend over the cached rows of the row's request. A bfloat16 cache goes through the
+    tensor-core form, portions of prompts in groups of 16 tokens per head and single tokens with their heads as the
+    group (the step's attention plan names both); the 32-bit path and other sizes go through the plain kernel."""
     pool = cache.k
+    plan = attention_plan(step) if USE_MMA_LATENT and pool.dtype == torch.bfloat16 else None
+    if plan is not None and latent_attention_mma_supported(rank, Dk):
+        lib = library.load()
+
+        def launch(row0, nrows, rows, n):
+            library.check(lib.cuca_latent_attention_mma(
+                _p(qk), _p(out), _p(pool), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
+                _p(cache.tables), cache.tables.shape[1], _p(row0), _p(nrows), _p(rows), n, H, rank, Dk, float(scale),
+                int(window or 0), _p(err), _stream()), "latent_attention_mma")
+        if plan.n_portions:
+            row0, nrows, n = plan.tiles(LATENT_TILE_ROWS)
+            launch(row0, nrows, None, n)
+        if plan.n_decode:
+            launch(None, None, plan.decode_rows, plan.n_decode)
+        return
     library.check(library.load().cuca_latent_attention(
         _p(qk), _p(out), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions),
         _p(step.seq_of_row), _p(cache.tables), cache.tables.shape[1], qk.shape[0], H, rank, Dk, float(scale),

@@ -54,6 +54,11 @@ CONFIGS = {
                     mamba2(heads=3, vdim=20, state=40, groups=3, conv=1, norm_groups=3),
                     latent(heads=5, dim=12, rot_dim=6, vdim=10, kv_rank=33, window=40, base=250000.0)],
                    width=80, vocab=257, ff=72, logit_scale=1.0, eps=1e-6),
+    # latent sizes that the tensor-core attention takes in bfloat16: 64 + 16 and 96 + 32 values per cached row, more
+    # heads than one group of 16 holds, a window that ends inside a key tile and none
+    "wide": config([latent(heads=5, dim=16, rot_dim=16, vdim=16, kv_rank=64, window=23, scale=0.6), mamba2(),
+                    latent(heads=18, dim=8, rot_dim=32, vdim=8, kv_rank=96, window=None, scale=0.5), mingru(24)],
+                   width=72, vocab=211, loop=(2, 4, 2)),
     "once": config([latent(window=17), mamba2(conv=7, state=6, groups=4, heads=4, vdim=12)], width=56, vocab=97,
                    loop=(0, 2, 1)),
 }

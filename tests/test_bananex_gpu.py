@@ -236,6 +236,54 @@ def test_latent_attention_alone_whole_and_cut(rt32, layer):
     assert int(rt32.err.item()) == 0
 
 
+@pytest.mark.parametrize("layer", [
+    bu.latent(heads=3, dim=16, rot_dim=16, vdim=24, kv_rank=64, window=20, scale=1.0),
+    bu.latent(heads=20, dim=8, rot_dim=32, vdim=8, kv_rank=96, window=None, scale=0.8),
+    bu.latent(heads=2, dim=24, rot_dim=16, vdim=12, kv_rank=256, window=70, scale=0.9),
+    bu.latent(heads=1, dim=8, rot_dim=64, vdim=8, kv_rank=512, window=130, scale=1.0),
+    bu.latent(heads=16, dim=16, rot_dim=0, vdim=8, kv_rank=32, window=64, scale=1.0)])
+def test_latent_attention_on_tensor_cores(layer):
+    """The bfloat16 forms: prompts in groups of 16 tokens per head, single tokens with their heads as the group.
+    Scales near one make the softmax pick few keys, so a key that is dropped, seen too early or too late moves
+    the result by far more than rounding does. 200 tokens walk windows over several key tiles and page borders."""
+    from cuca_b200.cache.device import CacheView
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.latent_attention import LatentAttention
+    from cuca_b200.runtime import Runtime
+    rt = Runtime("cuda:0", torch.bfloat16)
+    dev, E, eps, bs = rt.device, 48, 1e-5, 16
+    part = _part("latent_attention", LatentAttention, layer, rt, E, eps)
+    assert ops.latent_attention_mma_supported(part.rank, part.key_dim)
+    ws = {k: bu.bf16_round(v) for k, v in _weights_for(part, 11).items()}
+    needs = part.tensors()
+    part.load(lambda n: torch.tensor(ws[n], dtype=torch.float32 if needs[n].keep_fp32 else torch.bfloat16, device=dev))
+    part.prepare(256)
+    rs = np.random.default_rng(12)
+    xs = [bu.bf16_round(rs.normal(0, 1.5, (n, E))) for n in (200, 37)]
+    want = [pb.latent_attention(x, ws, "l0.mix.", layer["mixer"], eps) for x in xs]
+    pb.ROUND = bu.bf16_round
+    try:
+        rounded = [pb.latent_attention(x, ws, "l0.mix.", layer["mixer"], eps) for x in xs]
+    finally:
+        pb.ROUND = None
+    tol = [max(2e-2 * np.abs(b).max(), 4 * np.abs(a - b).max()) for a, b in zip(rounded, want)]
+    order = rs.permutation(20).tolist()
+    for cuts in ([CUTS[0]] * 2, [[150] + CUTS[1], CUTS[2]], [[3, 64, 17, 90] + CUTS[1], CUTS[1]]):
+        pool = torch.full((20, 1, bs, part.key_dim), float("nan"), dtype=torch.bfloat16, device=dev)
+        tables = torch.full((4, 16), -1, dtype=torch.int32, device=dev)
+        tables[1, :13] = torch.tensor(order[:13], dtype=torch.int32)
+        tables[3, :3] = torch.tensor(order[13:16], dtype=torch.int32)
+
+        def fwd(h, step):
+            stream = rt.stream(torch.zeros(h.shape[0], E, device=dev))  # few rows may leave slices pending on it
+            part.forward(h.to(torch.bfloat16), stream, step, CacheView(pool, None, tables, bs, 0, None, step.slots))
+            return stream.data
+        got = _run_cut(dev, fwd, xs, cuts, [1, 3], E)
+        for a, b, t in zip(got, want, tol):
+            assert np.isfinite(a).all() and np.abs(a - b).max() < t, (np.abs(a - b).max(), t)
+    assert int(rt.err.item()) == 0
+
+
 def test_dense_feed_forward_and_loop_entry_alone(rt32):
     from cuca_b200.parts.base import PartSpec
     from cuca_b200.parts.mlp import DenseActivation
@@ -263,7 +311,7 @@ def test_dense_feed_forward_and_loop_entry_alone(rt32):
 
 
 # ------------------------------------------------------------------------------------------ whole models
-LENGTHS = {"mix": [1, 2, 5, 16, 33, 64, 97, 130], "loop0": [3, 17, 48, 100], "flat": [2, 40, 41, 42, 90, 150],
+LENGTHS = {"wide": [1, 15, 16, 17, 63, 65, 140], "mix": [1, 2, 5, 16, 33, 64, 97, 130], "loop0": [3, 17, 48, 100], "flat": [2, 40, 41, 42, 90, 150],
            "once": [1, 18, 35, 77]}
 
 
