@@ -136,8 +136,9 @@ latent_attention_mma_kernel(Params p) {
 
   for (int kt = (lo_tile / KT) * KT; kt <= Pmax; kt += KT) {
     __syncthreads();  // the tile before is read to the end (and, the first time, the queries are written)
-    for (int e = threadIdx.x; e < KT * chunks; e += 128) {
-      const int j = e / chunks, ch = e - j * chunks;
+    {
+      // two threads per key: one page lookup each, then the row's 16-byte pieces in turn with nothing between them
+      const int j = threadIdx.x >> 1;
       const int kp = kt + j;
       bool valid = kp >= lo_tile && kp <= Pmax;
       const bf16* src = p.pool;
@@ -147,10 +148,11 @@ latent_attention_mma_kernel(Params p) {
           if (p.err) atomicExch(p.err, CUCA_ERR_BLOCK_RANGE);
           valid = false;
         } else {
-          src = p.pool + ((size_t)blk * p.bs + (kp % p.bs)) * Dk + ch * 8;
+          src = p.pool + ((size_t)blk * p.bs + (kp % p.bs)) * Dk;
         }
       }
-      cp_async16(ks_addr + (uint32_t)(j * RS + ch * 8) * 2, src, valid);
+      const uint32_t dst = ks_addr + (uint32_t)(j * RS) * 2;
+      for (int ch = threadIdx.x & 1; ch < chunks; ch += 2) cp_async16(dst + ch * 16, valid ? src + ch * 8 : p.pool, valid);
     }
     cp_async_commit();
     cp_async_wait_all();

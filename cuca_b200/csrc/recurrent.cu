@@ -26,15 +26,75 @@ __global__ void mingru_scan_kernel(const float* __restrict__ zxg, float* __restr
   const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
   if (slot < 0 || n <= 0 || c >= W) return;
   float S = state[(size_t)slot * W + c];
-  for (int t = 0; t < n; ++t) {
+  // eight tokens' inputs are requested before the first is used: the chain through S is short, the loads are not
+  constexpr int U = 8;
+  for (int t0 = 0; t0 < n; t0 += U) {
+    float zr[U], ur[U], gr[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      if (t0 + i < n) {
+        const float* row = zxg + (size_t)(r0 + t0 + i) * 3 * W;
+        zr[i] = row[c]; ur[i] = row[W + c]; gr[i] = row[2 * W + c];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      if (t0 + i < n) {
+        const float z = sigmoidf_(zr[i]);
+        const float u = ur[i];
+        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+        S = (1.f - z) * S + z * cand;
+        out[(size_t)(r0 + t0 + i) * W + c] = from_f32<TO>(S * siluf_(gr[i]));
+      }
+    }
+  }
+  state[(size_t)slot * W + c] = S;
+}
+
+// The same recurrence over long portions, cut into chunks of L tokens that run side by side: S_t = a_t S_(t-1) + b_t
+// with a = 1 - z, b = z c composes, so a chunk is summed up as (product of a, its own end state from zero), the
+// chunks' start states follow from those in one short pass per channel, and every chunk then runs from its start
+// state. phase 0: chunk sums into carry[q][k][0..1][c]; phase 1: start states into carry[q][k][0][c], the request's
+// state brought up to date; phase 2: the outputs. The start states are rounded differently than token by token.
+template <typename TO>
+__global__ void mingru_chunked_kernel(const float* __restrict__ zxg, float* __restrict__ state, float* __restrict__ carry,
+                                      TO* __restrict__ out, const int* __restrict__ req_row0,
+                                      const int* __restrict__ req_count, const int* __restrict__ slots, int W, int L,
+                                      int max_chunks, int phase) {
+  pdl_trigger();
+  pdl_wait();
+  const int q = blockIdx.z, k = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
+  if (slot < 0 || n <= 0 || c >= W) return;
+  const int n_chunks = (n + L - 1) / L;
+  float* cq = carry + (size_t)q * max_chunks * 2 * W;
+  if (phase == 1) {
+    float S = state[(size_t)slot * W + c];
+    for (int j = 0; j < n_chunks; ++j) {
+      const float a = cq[(size_t)(2 * j) * W + c], b = cq[(size_t)(2 * j + 1) * W + c];
+      cq[(size_t)(2 * j) * W + c] = S;
+      S = fmaf(a, S, b);
+    }
+    state[(size_t)slot * W + c] = S;
+    return;
+  }
+  if (k >= n_chunks) return;
+  const int t1 = (k + 1) * L < n ? (k + 1) * L : n;
+  float a = 1.f, S = phase == 0 ? 0.f : cq[(size_t)(2 * k) * W + c];
+  for (int t = k * L; t < t1; ++t) {
     const float* row = zxg + (size_t)(r0 + t) * 3 * W;
     const float z = sigmoidf_(row[c]);
     const float u = row[W + c];
     const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
     S = (1.f - z) * S + z * cand;
-    out[(size_t)(r0 + t) * W + c] = from_f32<TO>(S * siluf_(row[2 * W + c]));
+    if (phase == 0) a *= 1.f - z;
+    else out[(size_t)(r0 + t) * W + c] = from_f32<TO>(S * siluf_(row[2 * W + c]));
   }
-  state[(size_t)slot * W + c] = S;
+  if (phase == 0) {
+    cq[(size_t)(2 * k) * W + c] = a;
+    cq[(size_t)(2 * k + 1) * W + c] = S;
+  }
 }
 
 // in: 32-bit rows of stride ld_in, channel c at column col0 + c. kept: [slots, taps - 1, C] the inputs before the
@@ -89,56 +149,112 @@ __global__ void causal_conv_kernel(const float* __restrict__ in, int ld_in, int 
 
 constexpr int SSM_MAXR = 32;  // state values a thread holds
 
-// One block per (head, request). Thread (p, s): value column p, state rows s * nr .. s * nr + nr - 1. state:
-// [slots, H, P, N]. xbc: 32-bit [rows, H P + 2 G N] after the convolution (x | B | C); dt_raw: rows of stride ld_dt,
+// an asynchronous copy of 4 or 16 bytes from global to shared memory
+__device__ __forceinline__ void cp_async_f(float* dst, const float* src, int bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+// One block per (head, request, run of PB value columns). Thread (p, s): value column p, state rows s, s + NS,
+// s + 2 NS, ... (neighbouring threads read neighbouring shared-memory banks). state: [slots, H, P, N]. xbc: 32-bit [rows, H P + 2 G N] after the convolution (x | B | C); dt_raw: rows of stride ld_dt,
 // head h at column dt_col + h, before bias and softplus.
+template <int NR>  // state rows a thread holds at most (a compile-time bound keeps the recurrence's loop short)
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_raw, int ld_dt, int dt_col,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
                                 const int* __restrict__ req_row0, const int* __restrict__ req_count,
-                                const int* __restrict__ slots, int H, int P, int N, int G, int NS, int nr) {
+                                const int* __restrict__ slots, int H, int P, int N, int G, int NS, int TC, int PB) {
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, q = blockIdx.y;
   const int slot = slots[q], n = req_count[q], r0 = req_row0[q];
   if (slot < 0 || n <= 0) return;
-  const int p_raw = threadIdx.x / NS, s = threadIdx.x % NS;
-  const bool live = p_raw < P;
+  const int p_raw = blockIdx.z * PB + threadIdx.x / NS, s = threadIdx.x % NS;
+  const bool live = threadIdx.x / NS < PB && p_raw < P;
   const int p = live ? p_raw : P - 1;
-  const int n0 = s * nr;
   const int g = h / (H / G);
   const int C = H * P + 2 * G * N;
-  float S[SSM_MAXR];
+  float S[NR];
   float* st = state + (((size_t)slot * H + h) * P + p) * N;
 #pragma unroll
-  for (int i = 0; i < SSM_MAXR; ++i) S[i] = (i < nr && n0 + i < N) ? st[n0 + i] : 0.f;
+  for (int i = 0; i < NR; ++i) S[i] = (s + i * NS < N) ? st[s + i * NS] : 0.f;
   const float A = -expf(a_log[h]);
   const float bias = dt_bias[h], D = d_skip[h];
-  for (int t = 0; t < n; ++t) {
-    const size_t row = (size_t)(r0 + t);
-    const float v = dt_raw[row * ld_dt + dt_col + h] + bias;
-    const float dt = v > 20.f ? v : log1pf(expf(v));
-    const float decay = expf(A * dt);
-    const float* xr = xbc + row * C;
-    const float x = xr[h * P + p];
-    const float* Br = xr + H * P + g * N + n0;
-    const float* Cr = Br + G * N;
-    const float dx = dt * x;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < SSM_MAXR; ++i) {
-      if (i < nr && n0 + i < N) {
-        S[i] = fmaf(decay, S[i], dx * Br[i]);
-        acc = fmaf(S[i], Cr[i], acc);
+  // A token's inputs in shared memory: B [N], C [N], x [P], step size, decay; `per` floats, a multiple of four.
+  // Two runs of TC tokens: the next run's copies (cp.async) are in flight while this one is worked through.
+  const int span = 2 * N + P;
+  const int per = (span + 2 + 3) & ~3;
+  const bool vec4 = ((N | P | (H * P)) & 3) == 0;
+  auto stage = [&](int t0, int buf) {
+    const int nt = n - t0 < TC ? n - t0 : TC;
+    float* dst = sm + (size_t)buf * TC * per;
+    if (vec4) {
+      const int units = span >> 2;
+      for (int e = threadIdx.x; e < nt * units; e += blockDim.x) {
+        const int tt = e / units, i = (e - tt * units) << 2;
+        const int col = i < 2 * N ? H * P + g * N + i + (i >= N ? (G - 1) * N : 0) : h * P + (i - 2 * N);
+        cp_async_f(dst + tt * per + i, xbc + (size_t)(r0 + t0 + tt) * C + col, 16);
+      }
+    } else {
+      for (int e = threadIdx.x; e < nt * span; e += blockDim.x) {
+        const int tt = e / span, i = e - tt * span;
+        const int col = i < 2 * N ? H * P + g * N + i + (i >= N ? (G - 1) * N : 0) : h * P + (i - 2 * N);
+        cp_async_f(dst + tt * per + i, xbc + (size_t)(r0 + t0 + tt) * C + col, 4);
       }
     }
-    for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (live && s == 0) y[row * (H * P) + h * P + p] = acc + D * x;
+    for (int e = threadIdx.x; e < nt; e += blockDim.x)
+      cp_async_f(dst + e * per + span, dt_raw + (size_t)(r0 + t0 + e) * ld_dt + dt_col + h, 4);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(0, 0);
+  for (int t0 = 0, run = 0; t0 < n; t0 += TC, ++run) {
+    const int nt = n - t0 < TC ? n - t0 : TC;
+    float* cur = sm + (size_t)(run & 1) * TC * per;
+    if (t0 + TC < n) {
+      stage(t0 + TC, (run & 1) ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x < nt) {  // step size and decay of every token of the run, once
+      float* in = cur + threadIdx.x * per;
+      const float raw = in[span] + bias;
+      const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+      in[span] = dt;
+      in[span + 1] = expf(A * dt);
+    }
+    __syncthreads();
+    // (tokens only hang together through one multiply-add per state value: four of them are worked through at once)
+#pragma unroll 4
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* in = cur + tt * per;
+      const float dt = in[span], decay = in[span + 1];
+      const float x = in[2 * N + p];
+      const float* Br = in + s;
+      const float* Cr = in + N + s;
+      const float dx = dt * x;
+      // four partial sums, in an order that depends on the sizes alone
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < NR; ++i) {
+        if (s + i * NS < N) {
+          S[i] = fmaf(decay, S[i], dx * Br[i * NS]);
+          part[i & 3] = fmaf(S[i], Cr[i * NS], part[i & 3]);
+        }
+      }
+      float acc = (part[0] + part[1]) + (part[2] + part[3]);
+      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && s == 0) y[(size_t)(r0 + t0 + tt) * (H * P) + h * P + p] = acc + D * x;
+    }
+    __syncthreads();  // this run is read to the end before the run after next is copied over it
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < SSM_MAXR; ++i)
-      if (i < nr && n0 + i < N) st[n0 + i] = S[i];
+    for (int i = 0; i < NR; ++i)
+      if (s + i * NS < N) st[s + i * NS] = S[i];
   }
 }
 
@@ -189,6 +305,29 @@ CUCA_API int cuca_mingru_scan(const float* zxg, float* state, void* out, int out
   return 0;
 }
 
+// Long portions in chunks of `L` tokens side by side (see the kernel). carry: [n_seqs, max_chunks, 2, W] 32-bit
+// scratch, max_chunks >= ceil(longest portion / L).
+CUCA_API int cuca_mingru_scan_chunked(const float* zxg, float* state, float* carry, void* out, int out_dtype,
+                                      const int* req_row0, const int* req_count, const int* slots, int n_seqs, int W,
+                                      int L, int max_chunks, cudaStream_t stream) {
+  if (n_seqs == 0) return 0;
+  CUCA_REQUIRE(W > 0 && L > 0 && max_chunks > 0 && n_seqs <= 65535 && max_chunks <= 65535,
+               "mingru_scan_chunked: bad sizes W=%d L=%d chunks=%d requests=%d", W, L, max_chunks, n_seqs);
+  for (int phase = 0; phase < 3; ++phase) {
+    dim3 grid((W + 127) / 128, phase == 1 ? 1 : max_chunks, n_seqs);
+    if (out_dtype == CUCA_F32)
+      cuca_launch(mingru_chunked_kernel<float>, grid, dim3(128), 0, stream, true, zxg, state, carry, (float*)out,
+                  req_row0, req_count, slots, W, L, max_chunks, phase);
+    else if (out_dtype == CUCA_BF16)
+      cuca_launch(mingru_chunked_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, true, zxg, state, carry,
+                  (__nv_bfloat16*)out, req_row0, req_count, slots, W, L, max_chunks, phase);
+    else
+      CUCA_REQUIRE(false, "mingru_scan_chunked: unknown dtype %d", out_dtype);
+    CUCA_CHECK_LAUNCH("mingru_scan_chunked");
+  }
+  return 0;
+}
+
 CUCA_API int cuca_causal_conv(const float* in, int ld_in, int col0, const void* w, const void* bias, int w_dtype,
                               float* kept, float* out, const int* seq_of_row, const int* req_row0,
                               const int* req_count, const int* slots, int n_rows, int n_seqs, int C, int taps,
@@ -215,7 +354,7 @@ CUCA_API int cuca_ssm_scan_split(int P, int N, int* ns_out, int* nr_out) {
   int ns = 1;
   while ((N + ns - 1) / ns > SSM_MAXR && ns < 32) ns <<= 1;
   if ((N + ns - 1) / ns > SSM_MAXR) return 1;
-  while (ns < 32 && ns * 2 <= N && P * ns * 2 <= 256) ns <<= 1;
+  while (ns < 16 && ns * 4 <= N) ns <<= 1;  // at least four state rows a thread, at most sixteen threads a column
   *ns_out = ns;
   *nr_out = (N + ns - 1) / ns;
   return 0;
@@ -231,10 +370,24 @@ CUCA_API int cuca_ssm_scan(const float* xbc, const float* dt_raw, int ld_dt, int
   CUCA_REQUIRE(n_seqs <= 65535, "ssm_scan: %d requests exceed the launch limit", n_seqs);
   int ns, nr;
   CUCA_REQUIRE(cuca_ssm_scan_split(P, N, &ns, &nr) == 0, "ssm_scan: state size %d exceeds %d", N, 32 * SSM_MAXR);
-  const int threads = (P * ns + 31) / 32 * 32;
-  CUCA_REQUIRE(threads <= 1024, "ssm_scan: value size %d with %d threads per column exceeds a block", P, ns);
-  cuca_launch(ssm_scan_kernel, dim3(H, n_seqs), dim3(threads), 0, stream, true, xbc, dt_raw, ld_dt, dt_col, dt_bias,
-              a_log, d_skip, state, y, req_row0, req_count, slots, H, P, N, G, ns, nr);
+  // value columns of a block: what fills 128 threads, so that a head's columns spread over several SMs
+  int pb = 128 / ns;
+  pb = pb < 1 ? 1 : (pb > P ? P : pb);
+  const int threads = (pb * ns + 31) / 32 * 32;
+  // tokens whose inputs are staged together: two runs of as many as 44 KB of shared memory hold, 16 at most
+  const int per = (2 * N + P + 2 + 3) & ~3;
+  int tc = 45056 / (2 * per * 4);
+  tc = tc > 16 ? 16 : tc;
+  CUCA_REQUIRE(tc >= 1, "ssm_scan: state size %d and value size %d exceed a token's shared memory", N, P);
+#define SSM(NR)                                                                                                    \
+  cuca_launch(ssm_scan_kernel<NR>, dim3(H, n_seqs, (P + pb - 1) / pb), dim3(threads), (size_t)2 * tc * per * 4, stream, \
+              true, xbc, dt_raw, ld_dt, dt_col, dt_bias, a_log, d_skip, state, y, req_row0, req_count, slots, H, P, \
+              N, G, ns, tc, pb)
+  if (nr <= 4) SSM(4);
+  else if (nr <= 8) SSM(8);
+  else if (nr <= 16) SSM(16);
+  else SSM(32);
+#undef SSM
   CUCA_CHECK_LAUNCH("ssm_scan");
   return 0;
 }

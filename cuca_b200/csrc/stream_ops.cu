@@ -91,17 +91,26 @@ post_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const f
   for (int i = threadIdx.x; i < E; i += NT) out[row * E + i] = from_f32<TO>(xr[i] * ix * gain2[i * gain2_stride]);
 }
 
+__device__ __forceinline__ float gelu_of(float z, int tanh_form) {
+  if (tanh_form) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+}
+
+// 16 bytes per thread and round where the tensor allows it (n_vec pieces), the rest value by value
 template <typename T>
-__global__ void gelu_kernel(T* __restrict__ a, size_t n, int tanh_form) {
+__global__ void gelu_kernel(T* __restrict__ a, size_t n, size_t n_vec, int tanh_form) {
   pdl_trigger();
   pdl_wait();
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float z = to_f32(a[i]);
-    float r;
-    if (tanh_form) r = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    else r = 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
-    a[i] = from_f32<T>(r);
+  constexpr int PER = 16 / sizeof(T);
+  const size_t stride = (size_t)gridDim.x * blockDim.x, first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (size_t i = first; i < n_vec; i += stride) {
+    uint4 w = reinterpret_cast<uint4*>(a)[i];
+    T* v = reinterpret_cast<T*>(&w);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) v[k] = from_f32<T>(gelu_of(to_f32(v[k]), tanh_form));
+    reinterpret_cast<uint4*>(a)[i] = w;
   }
+  for (size_t i = n_vec * PER + first; i < n; i += stride) a[i] = from_f32<T>(gelu_of(to_f32(a[i]), tanh_form));
 }
 
 __global__ void scale_kernel(float* __restrict__ a, size_t n, float s) {
@@ -174,11 +183,16 @@ CUCA_API int cuca_post_norm_add(float* x, const float* y, const float* gain, int
 // a = gelu(a) in place: the exact form (erf), or the tanh form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
 CUCA_API int cuca_gelu(void* a, int dtype, size_t n, int tanh_form, cudaStream_t stream) {
   if (n == 0) return 0;
-  if (dtype == CUCA_F32)
-    cuca_launch(gelu_kernel<float>, dim3(flat_grid(n, 256)), dim3(256), 0, stream, true, (float*)a, n, tanh_form);
-  else if (dtype == CUCA_BF16)
-    cuca_launch(gelu_kernel<__nv_bfloat16>, dim3(flat_grid(n, 256)), dim3(256), 0, stream, true, (__nv_bfloat16*)a, n,
+  const bool aligned = (((size_t)a) & 15) == 0;
+  if (dtype == CUCA_F32) {
+    const size_t nv = aligned ? n / 4 : 0;
+    cuca_launch(gelu_kernel<float>, dim3(flat_grid(nv > 0 ? nv : n, 256)), dim3(256), 0, stream, true, (float*)a, n, nv,
                 tanh_form);
+  } else if (dtype == CUCA_BF16) {
+    const size_t nv = aligned ? n / 8 : 0;
+    cuca_launch(gelu_kernel<__nv_bfloat16>, dim3(flat_grid(nv > 0 ? nv : n, 256)), dim3(256), 0, stream, true,
+                (__nv_bfloat16*)a, n, nv, tanh_form);
+  }
   else
     CUCA_REQUIRE(false, "gelu: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("gelu");

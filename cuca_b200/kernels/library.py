@@ -73,6 +73,7 @@ _SIGNATURES = {
     "cuca_scale": [_P, c_size_t, _F, _P],
     "cuca_concat2": [_P, _P, _P, _I, _I, _I, _P],
     "cuca_mingru_scan": [_P, _P, _P, _I, _P, _P, _P, _I, _I, _P],
+    "cuca_mingru_scan_chunked": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "cuca_causal_conv": [_P, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "cuca_ssm_scan": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_gated_group_norm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _P],

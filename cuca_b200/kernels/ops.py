@@ -672,8 +672,23 @@ def concat2(a, b, out) -> None:
 
 
 # ------------------------------------------------------------------ recurrent mixers
+MINGRU_CHUNK = 32  # tokens of a chunk where long portions run as chunks side by side
+MINGRU_CHUNKED_FROM = 256  # portions at least this long, in the serving precision only
+
+
 def mingru_scan(zxg, state, out, step) -> None:
+    """The gated recurrence along every request's rows. Token by token in order (the 32-bit path always: its bits do
+    not depend on how a prompt was cut); in bfloat16 a step with a long portion runs chunks of the portions side by
+    side and carries the state across them in a short pass."""
     _cuda(zxg, state, out)
+    counts = step.host.get("counts") if step.static_max_len is None else None
+    if out.dtype == torch.bfloat16 and counts and max(counts) >= MINGRU_CHUNKED_FROM:
+        max_chunks = -(-max(counts) // MINGRU_CHUNK)
+        carry = torch.empty(step.n_seqs, max_chunks, 2, out.shape[1], dtype=torch.float32, device=out.device)
+        library.check(library.load().cuca_mingru_scan_chunked(
+            _p(zxg), _p(state), _p(carry), _p(out), dtype_code(out.dtype), _p(step.req_row0), _p(step.req_count),
+            _p(step.slots), step.n_seqs, out.shape[1], MINGRU_CHUNK, max_chunks, _stream()), "mingru_scan_chunked")
+        return
     library.check(library.load().cuca_mingru_scan(_p(zxg), _p(state), _p(out), dtype_code(out.dtype),
                                                   _p(step.req_row0), _p(step.req_count), _p(step.slots), step.n_seqs,
                                                   out.shape[1], _stream()), "mingru_scan")

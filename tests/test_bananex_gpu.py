@@ -176,6 +176,34 @@ def test_mingru_alone_whole_and_cut(rt32, inner):
             assert np.abs(a - b).max() < 2e-5 * max(1.0, np.abs(b).max())
 
 
+def test_mingru_long_portions_in_chunks():
+    """In bfloat16 a portion of 256 tokens or more runs as chunks side by side with the state carried across
+    them: whole, and cut so that a chunked portion starts from a state that single tokens left."""
+    from cuca_b200.cache.device import CacheView
+    from cuca_b200.kernels import ops
+    from cuca_b200.parts.recurrent import MinGRU
+    from cuca_b200.runtime import Runtime
+    rt = Runtime("cuda:0", torch.bfloat16)
+    dev, E, inner = rt.device, 40, 70
+    part = _part("mingru", MinGRU, bu.mingru(inner), rt, E, 1e-5)
+    ws = {k: bu.bf16_round(v) for k, v in _weights_for(part, 3).items()}
+    part.load(lambda n: torch.tensor(ws[n], dtype=torch.bfloat16, device=dev))
+    rs = np.random.default_rng(4)
+    xs = [bu.bf16_round(rs.normal(0, 1.5, (n, E))) for n in (700, 300)]
+    want = [pb.mingru(x, ws, "l0.mix.", {"width": inner}) for x in xs]
+    assert ops.MINGRU_CHUNKED_FROM <= 256
+    for cuts in ([CUTS[0]] * 2, [[1, 1, 3, 290, 1, 1, 1000], [260, 1, 1000]]):
+        state = torch.zeros(4, inner, device=dev)
+
+        def fwd(h, step):
+            stream = rt.stream(torch.zeros(h.shape[0], E, device=dev))
+            part.forward(h.to(torch.bfloat16), stream, step, CacheView(None, None, None, 16, -1, {"mingru": state}, step.slots))
+            return stream.data
+        got = _run_cut(dev, fwd, xs, cuts, [2, 1], E)
+        for a, b in zip(got, want):
+            assert np.abs(a - b).max() < 3e-2 * np.abs(b).max()
+
+
 @pytest.mark.parametrize("layer", [bu.mamba2(), bu.mamba2(heads=3, vdim=20, state=40, groups=3, conv=1, norm_groups=3),
                                    bu.mamba2(heads=2, vdim=64, state=128, groups=1, conv=7, norm_groups=1),
                                    bu.mamba2(heads=4, vdim=12, state=6, groups=4, conv=2, norm_groups=4)])
@@ -390,6 +418,17 @@ def test_long_decoding_past_every_window(models):
     for dtype in ("float32", "bfloat16"):
         got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=8, window_pools="sized")
         ru.compare(steps, got, reqs, oracle, oracle.tolerance(dtype, reqs))
+
+
+def test_long_prompts(models):
+    """Prompts long enough for the forms that only long portions take (chunks of the gated recurrence side by side,
+    many key tiles per group of the tensor-core attention), whole and in portions that start inside a chunk."""
+    folder, cfg, oracle = models["wide"]
+    reqs = {"p": bu.random_tokens(610, cfg["vocab"], 8), "q": bu.random_tokens(300, cfg["vocab"], 9)}
+    for steps in (ru.trace_whole(reqs), ru.trace_portions(reqs, sizes=(7, 300, 2, 280, 1, 64))):
+        for dtype in ("bfloat16", "float32"):
+            got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=16)
+            ru.compare(steps, got, reqs, oracle, oracle.tolerance(dtype, reqs))
 
 
 def test_trace_run_as_a_program(models):
