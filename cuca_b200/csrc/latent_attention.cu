@@ -137,6 +137,42 @@ head_linear_kernel(const float* __restrict__ a, int lda, int a_head, const TW* _
   }
 }
 
+// The same contraction for up to 16 rows (single decoded tokens): a warp per (head, output) reads its weight row once
+// and keeps a sum per row; the lanes split K. Used in the serving precision only: its sums run in another order
+// than the tiled kernel's.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(128)
+head_linear_rows_kernel(const float* __restrict__ a, int lda, int a_head, const TW* __restrict__ w,
+                        TO* __restrict__ out, int ldo, int o_head, const float* __restrict__ gate, int ldg, int T,
+                        int N, int K) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 4 + (threadIdx.x >> 5), h = blockIdx.y;
+  if (n >= N) return;
+  float acc[16];
+#pragma unroll
+  for (int t = 0; t < 16; ++t) acc[t] = 0.f;
+  const TW* wr = w + ((size_t)h * N + n) * K;
+  const float* ah = a + (size_t)h * a_head;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f32(wr[k]);
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+      if (t < T) acc[t] = fmaf(ah[(size_t)t * lda + k], wv, acc[t]);
+  }
+#pragma unroll
+  for (int t = 0; t < 16; ++t) {
+    if (t < T) {
+      float v = warp_sum(acc[t]);
+      if (lane == 0) {
+        if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)t * ldg + (size_t)h * N + n]));
+        out[(size_t)t * ldo + (size_t)h * o_head + n] = from_f32<TO>(v);
+      }
+    }
+  }
+}
+
 // One warp per (row, head). qk: [rows, H, Dk] 32-bit; pool rows [Dk] per position; out: [rows, H, rank] 32-bit, the
 // softmax-weighted sum of the first `rank` values of the visible cache rows. NACC * 32 >= rank.
 template <typename TC, int NACC>
@@ -245,6 +281,19 @@ CUCA_API int cuca_head_linear(const float* a, int lda, int a_head, const void* w
                               int K, cudaStream_t stream) {
   if (T == 0) return 0;
   CUCA_REQUIRE(H > 0 && N > 0 && K > 0 && H <= 65535, "head_linear: bad sizes heads=%d out=%d in=%d", H, N, K);
+  if (T <= 16 && w_dtype == CUCA_BF16) {
+    dim3 rows_grid((N + 3) / 4, H);
+    if (out_dtype == CUCA_F32)
+      cuca_launch(head_linear_rows_kernel<__nv_bfloat16, float>, rows_grid, dim3(128), 0, stream, true, a, lda, a_head,
+                  (const __nv_bfloat16*)w, (float*)out, ldo, o_head, gate, ldg, T, N, K);
+    else if (out_dtype == CUCA_BF16)
+      cuca_launch(head_linear_rows_kernel<__nv_bfloat16, __nv_bfloat16>, rows_grid, dim3(128), 0, stream, true, a, lda,
+                  a_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, o_head, gate, ldg, T, N, K);
+    else
+      CUCA_REQUIRE(false, "head_linear: unsupported dtypes %d/%d", w_dtype, out_dtype);
+    CUCA_CHECK_LAUNCH("head_linear");
+    return 0;
+  }
   dim3 grid((N + 63) / 64, (T + 63) / 64, H);
   CUCA_REQUIRE(grid.y <= 65535, "head_linear: %d rows exceed the launch limit", T);
 #define HL(TW, TO)                                                                                               \

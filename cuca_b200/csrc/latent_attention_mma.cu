@@ -64,6 +64,11 @@ struct Params {
   int window;
   int TQ, HB;             // tokens x heads of a group, TQ * HB = 16
   int* err;
+  // Single tokens with few groups: the key tiles of a group are dealt to n_splits CTAs (blockIdx.z), each leaves its
+  // unnormalised sums, maximum and row sum, and `latent_merge_kernel` puts them together in split order.
+  int n_splits;
+  float* part_acc;        // [groups, head blocks, n_splits, 16, rank]
+  float* part_ml;         // [groups, head blocks, n_splits, 16, 2]: maximum (of scores times log2 e), row sum
 };
 
 // NT8: most 8-column output tiles a warp owns (rank / 4 / 8 of them are used)
@@ -134,7 +139,16 @@ latent_attention_mma_kernel(Params p) {
   const int b_key = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
   const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
 
-  for (int kt = (lo_tile / KT) * KT; kt <= Pmax; kt += KT) {
+  int kt_first = (lo_tile / KT) * KT, kt_last = Pmax;
+  if (p.n_splits > 1) {
+    const int tiles = (Pmax / KT) - (lo_tile / KT) + 1;
+    const int each = (tiles + p.n_splits - 1) / p.n_splits;
+    kt_first += (int)blockIdx.z * each * KT;
+    const int end = kt_first + each * KT - 1;
+    kt_last = end < Pmax ? end : Pmax;
+  }
+  __syncthreads();  // the queries are written (a split without tiles goes straight to the end)
+  for (int kt = kt_first; kt <= kt_last; kt += KT) {
     __syncthreads();  // the tile before is read to the end (and, the first time, the queries are written)
     {
       // two threads per key: one page lookup each, then the row's 16-byte pieces in turn with nothing between them
@@ -258,6 +272,26 @@ latent_attention_mma_kernel(Params p) {
     wsum[warp * 16 + g + 8] = l[1];
   }
   __syncthreads();
+  if (p.n_splits > 1) {
+    const size_t cell = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * p.n_splits + blockIdx.z;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = g + 8 * i;
+      float* o = p.part_acc + (cell * 16 + r) * rank + warp * DW;
+#pragma unroll
+      for (int n = 0; n < NT8; ++n) {
+        if (n < ntiles) {
+          o[n * 8 + 2 * t] = acc[n][2 * i];
+          o[n * 8 + 2 * t + 1] = acc[n][2 * i + 1];
+        }
+      }
+      if (warp == 0 && t == 0) {
+        p.part_ml[(cell * 16 + r) * 2] = m[i];
+        p.part_ml[(cell * 16 + r) * 2 + 1] = wsum[r] + wsum[16 + r] + wsum[32 + r] + wsum[48 + r];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (!rvalid[i]) continue;
@@ -273,6 +307,35 @@ latent_attention_mma_kernel(Params p) {
         o[n * 8 + 2 * t + 1] = acc[n][2 * i + 1] * inv;
       }
     }
+  }
+}
+
+// One block per (group, head block, row of 16): out = sum_z acc_z 2^(m_z - M) / sum_z l_z 2^(m_z - M), z in order.
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                    float* __restrict__ out, const int* __restrict__ rows,
+                                    const int* __restrict__ seq_of_row, int n_splits, int H, int rank) {
+  pdl_trigger();
+  pdl_wait();
+  const int grp = blockIdx.x, hb = blockIdx.y, r = blockIdx.z;
+  const int row = rows ? rows[grp] : grp;
+  const int head = hb * 16 + r;
+  if (head >= H || seq_of_row[row] < 0) return;
+  const size_t cell0 = ((size_t)grp * gridDim.y + hb) * n_splits;
+  float M = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((cell0 + z) * 16 + r) * 2]);
+  float L = 0.f;
+  for (int z = 0; z < n_splits; ++z) {
+    const float mz = part_ml[((cell0 + z) * 16 + r) * 2];
+    if (mz != -INFINITY) L += part_ml[((cell0 + z) * 16 + r) * 2 + 1] * exp2f(mz - M);
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float a = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float mz = part_ml[((cell0 + z) * 16 + r) * 2];
+      if (mz != -INFINITY) a += part_acc[((cell0 + z) * 16 + r) * rank + c] * exp2f(mz - M);
+    }
+    out[((size_t)row * H + head) * rank + c] = a * inv;
   }
 }
 
@@ -293,7 +356,8 @@ int launch(const Params& p, int n_groups, int head_blocks, cudaStream_t stream) 
     }
     configured = smem;
   }
-  cuca_launch(latent_attention_mma_kernel<NT8>, dim3(n_groups, head_blocks), dim3(128), smem, stream, true, p);
+  cuca_launch(latent_attention_mma_kernel<NT8>, dim3(n_groups, head_blocks, p.n_splits), dim3(128), smem, stream,
+              true, p);
   return 0;
 }
 
@@ -309,8 +373,8 @@ CUCA_API int cuca_latent_attention_mma_supported(int rank, int Dk) {
 CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* pool, int n_blocks, int bs,
                                        const int* positions, const int* seq_of_row, const int* tables,
                                        int table_stride, const int* tile_row0, const int* tile_nrows, const int* rows,
-                                       int n_groups, int H, int rank, int Dk, float scale, int window, int* err,
-                                       cudaStream_t stream) {
+                                       int n_groups, int H, int rank, int Dk, float scale, int window, int n_splits,
+                                       float* part_acc, float* part_ml, int* err, cudaStream_t stream) {
   if (n_groups == 0) return 0;
   CUCA_REQUIRE(cuca_latent_attention_mma_supported(rank, Dk), "latent_attention_mma: sizes rank=%d Dk=%d are not taken",
                rank, Dk);
@@ -319,6 +383,9 @@ CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* 
   p.seq_of_row = seq_of_row; p.tables = tables; p.table_stride = table_stride; p.tile_row0 = tile_row0;
   p.tile_nrows = tile_nrows; p.rows = rows; p.H = H; p.rank = rank; p.Dk = Dk;
   p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.err = err;
+  p.n_splits = (tile_row0 == nullptr && n_splits > 1 && part_acc && part_ml) ? n_splits : 1;
+  p.part_acc = part_acc; p.part_ml = part_ml;
+  CUCA_REQUIRE(p.n_splits <= 64, "latent_attention_mma: %d splits exceed 64", n_splits);
   const bool portions = tile_row0 != nullptr;
   p.TQ = portions ? 16 : 1;
   p.HB = portions ? 1 : 16;
@@ -331,5 +398,10 @@ CUCA_API int cuca_latent_attention_mma(const float* qk, float* out, const void* 
   else rc = launch<16>(p, n_groups, head_blocks, stream);
   if (rc) return rc;
   CUCA_CHECK_LAUNCH("latent_attention_mma");
+  if (p.n_splits > 1) {
+    cuca_launch(latent_merge_kernel, dim3(n_groups, head_blocks, 16), dim3(128), 0, stream, true,
+                (const float*)part_acc, (const float*)part_ml, out, rows, seq_of_row, p.n_splits, H, rank);
+    CUCA_CHECK_LAUNCH("latent_merge");
+  }
   return 0;
 }

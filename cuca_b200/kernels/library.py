@@ -83,7 +83,8 @@ _SIGNATURES = {
     "cuca_head_linear": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P],
     "cuca_latent_attention": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "cuca_latent_attention_mma_supported": [_I, _I],
-    "cuca_latent_attention_mma": [_P, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
+    "cuca_latent_attention_mma": [_P, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P,
+                                  _P, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }
 

@@ -762,16 +762,27 @@ def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> N
     if plan is not None and latent_attention_mma_supported(rank, Dk):
         lib = library.load()
 
-        def launch(row0, nrows, rows, n):
+        def launch(row0, nrows, rows, n, splits=1, acc=None, ml=None):
             library.check(lib.cuca_latent_attention_mma(
                 _p(qk), _p(out), _p(pool), pool.shape[0], pool.shape[2], _p(step.positions), _p(step.seq_of_row),
                 _p(cache.tables), cache.tables.shape[1], _p(row0), _p(nrows), _p(rows), n, H, rank, Dk, float(scale),
-                int(window or 0), _p(err), _stream()), "latent_attention_mma")
+                int(window or 0), splits, _p(acc), _p(ml), _p(err), _stream()), "latent_attention_mma")
         if plan.n_portions:
             row0, nrows, n = plan.tiles(LATENT_TILE_ROWS)
             launch(row0, nrows, None, n)
         if plan.n_decode:
-            launch(None, None, plan.decode_rows, plan.n_decode)
+            # single tokens: few groups (one per token and 16 heads), so a group's key tiles are dealt to several
+            # CTAs where that fills more of the GPU, and a second launch merges what they leave
+            keys = plan.max_len if not window else min(plan.max_len, int(window) + 1)
+            tiles = -(-keys // 64) + 1
+            cells = plan.n_decode * -(-H // 16)
+            splits = max(1, min(tiles, 2 * sm_count() // max(1, cells), 16))
+            if splits > 1:
+                acc = torch.empty(cells * splits * 16 * rank, dtype=torch.float32, device=out.device)
+                ml = torch.empty(cells * splits * 16 * 2, dtype=torch.float32, device=out.device)
+                launch(None, None, plan.decode_rows, plan.n_decode, splits, acc, ml)
+            else:
+                launch(None, None, plan.decode_rows, plan.n_decode)
         return
     library.check(library.load().cuca_latent_attention(
         _p(qk), _p(out), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions),
