@@ -155,6 +155,8 @@ head_linear_rows_kernel(const float* __restrict__ a, int lda, int a_head, const 
   for (int t = 0; t < 16; ++t) acc[t] = 0.f;
   const TW* wr = w + ((size_t)h * N + n) * K;
   const float* ah = a + (size_t)h * a_head;
+  // four steps of K at once: their loads are in flight together (the kernel is all latency at these sizes)
+#pragma unroll 4
   for (int k = lane; k < K; k += 32) {
     const float wv = to_f32(wr[k]);
 #pragma unroll

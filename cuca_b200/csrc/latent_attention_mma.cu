@@ -310,7 +310,8 @@ latent_attention_mma_kernel(Params p) {
   }
 }
 
-// One block per (group, head block, row of 16): out = sum_z acc_z 2^(m_z - M) / sum_z l_z 2^(m_z - M), z in order.
+// One block per (group, head block, row of 16): out = sum_z acc_z 2^(m_z - M) / sum_z l_z 2^(m_z - M), z in order
+// (up to 64 splits).
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     float* __restrict__ out, const int* __restrict__ rows,
                                     const int* __restrict__ seq_of_row, int n_splits, int H, int rank) {
@@ -321,21 +322,34 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const fl
   const int head = hb * 16 + r;
   if (head >= H || seq_of_row[row] < 0) return;
   const size_t cell0 = ((size_t)grp * gridDim.y + hb) * n_splits;
-  float M = -INFINITY;
-  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, part_ml[((cell0 + z) * 16 + r) * 2]);
-  float L = 0.f;
-  for (int z = 0; z < n_splits; ++z) {
-    const float mz = part_ml[((cell0 + z) * 16 + r) * 2];
-    if (mz != -INFINITY) L += part_ml[((cell0 + z) * 16 + r) * 2 + 1] * exp2f(mz - M);
+  __shared__ float wz[64];  // every split's weight 2^(m_z - M) / L, worked out once by the first warp
+  if (threadIdx.x < 32) {
+    float mz[2], lz[2];
+    float M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int z = threadIdx.x + 32 * k;
+      mz[k] = z < n_splits ? part_ml[((cell0 + z) * 16 + r) * 2] : -INFINITY;
+      lz[k] = z < n_splits ? part_ml[((cell0 + z) * 16 + r) * 2 + 1] : 0.f;
+      M = fmaxf(M, mz[k]);
+    }
+    M = warp_max(M);
+    float e[2], L = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      e[k] = mz[k] == -INFINITY ? 0.f : exp2f(mz[k] - M);
+      L += lz[k] * e[k];
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    wz[threadIdx.x] = e[0] * inv;
+    wz[threadIdx.x + 32] = e[1] * inv;
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  __syncthreads();
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float a = 0.f;
-    for (int z = 0; z < n_splits; ++z) {
-      const float mz = part_ml[((cell0 + z) * 16 + r) * 2];
-      if (mz != -INFINITY) a += part_acc[((cell0 + z) * 16 + r) * rank + c] * exp2f(mz - M);
-    }
-    out[((size_t)row * H + head) * rank + c] = a * inv;
+    for (int z = 0; z < n_splits; ++z) a = fmaf(part_acc[((cell0 + z) * 16 + r) * rank + c], wz[z], a);
+    out[((size_t)row * H + head) * rank + c] = a;
   }
 }
 

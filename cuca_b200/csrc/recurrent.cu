@@ -269,9 +269,28 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z
   const size_t row = blockIdx.y;
   const int c0 = blockIdx.x * part;
   float s = 0.f;
-  for (int i = threadIdx.x; i < part; i += 256) {
-    const float v = y[row * inner + c0 + i] * siluf_(z[row * ld_z + c0 + i]);
-    s = fmaf(v, v, s);
+  // parts of up to 4096 values stay in registers between the two passes (all loads of the row in flight together)
+  constexpr int KEEP = 16;
+  float kept[KEEP];
+  const bool keep = part <= KEEP * 256;
+  if (keep) {
+    float yv[KEEP], zv[KEEP];
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < part) { yv[k] = y[row * inner + c0 + i]; zv[k] = z[row * ld_z + c0 + i]; }
+    }
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int i = threadIdx.x + k * 256;
+      kept[k] = i < part ? yv[k] * siluf_(zv[k]) : 0.f;
+      s = fmaf(kept[k], kept[k], s);
+    }
+  } else {
+    for (int i = threadIdx.x; i < part; i += 256) {
+      const float v = y[row * inner + c0 + i] * siluf_(z[row * ld_z + c0 + i]);
+      s = fmaf(v, v, s);
+    }
   }
   s = warp_sum(s);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
@@ -280,6 +299,14 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += red[i];
   const float inv = rsqrtf(tot / (float)part + eps);
+  if (keep) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < part) out[row * inner + c0 + i] = from_f32<TO>(kept[k] * inv * to_f32(w[c0 + i]));
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < part; i += 256) {
     const float v = y[row * inner + c0 + i] * siluf_(z[row * ld_z + c0 + i]);
     out[row * inner + c0 + i] = from_f32<TO>(v * inv * to_f32(w[c0 + i]));
