@@ -159,12 +159,17 @@ __device__ __forceinline__ void cp_async_f(float* dst, const float* src, int byt
 // One block per (head, request, run of PB value columns). Thread (p, s): value column p, state rows s, s + NS,
 // s + 2 NS, ... (neighbouring threads read neighbouring shared-memory banks). state: [slots, H, P, N]. xbc: 32-bit [rows, H P + 2 G N] after the convolution (x | B | C); dt_raw: rows of stride ld_dt,
 // head h at column dt_col + h, before bias and softplus.
-template <int NR>  // state rows a thread holds at most (a compile-time bound keeps the recurrence's loop short)
+// NR: state rows a thread holds at most. NST: threads per value column when that is known at compile time and divides
+// the state evenly into NR rows each (the recurrence's loop is then free of index arithmetic and predicates: the
+// kernel is bound by how many instructions it issues); 0: the number comes at run time and rows are checked.
+template <int NR, int NST>
 __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt_raw, int ld_dt, int dt_col,
                                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 const float* __restrict__ d_skip, float* __restrict__ state, float* __restrict__ y,
                                 const int* __restrict__ req_row0, const int* __restrict__ req_count,
-                                const int* __restrict__ slots, int H, int P, int N, int G, int NS, int TC, int PB) {
+                                const int* __restrict__ slots, int H, int P, int N, int G, int NS_rt, int TC,
+                                int PB) {
+  const int NS = NST ? NST : NS_rt;
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
@@ -179,7 +184,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
   float S[NR];
   float* st = state + (((size_t)slot * H + h) * P + p) * N;
 #pragma unroll
-  for (int i = 0; i < NR; ++i) S[i] = (s + i * NS < N) ? st[s + i * NS] : 0.f;
+  for (int i = 0; i < NR; ++i) S[i] = (NST || s + i * NS < N) ? st[s + i * NS] : 0.f;
   const float A = -expf(a_log[h]);
   const float bias = dt_bias[h], D = d_skip[h];
   // A token's inputs in shared memory: B [N], C [N], x [P], step size, decay; `per` floats, a multiple of four.
@@ -240,7 +245,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
       float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < NR; ++i) {
-        if (s + i * NS < N) {
+        if (NST || s + i * NS < N) {
           S[i] = fmaf(decay, S[i], dx * Br[i * NS]);
           part[i & 3] = fmaf(S[i], Cr[i * NS], part[i & 3]);
         }
@@ -254,7 +259,7 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, const float* __re
   if (live) {
 #pragma unroll
     for (int i = 0; i < NR; ++i)
-      if (s + i * NS < N) st[s + i * NS] = S[i];
+      if (NST || s + i * NS < N) st[s + i * NS] = S[i];
   }
 }
 
@@ -406,14 +411,26 @@ CUCA_API int cuca_ssm_scan(const float* xbc, const float* dt_raw, int ld_dt, int
   int tc = 45056 / (2 * per * 4);
   tc = tc > 16 ? 16 : tc;
   CUCA_REQUIRE(tc >= 1, "ssm_scan: state size %d and value size %d exceed a token's shared memory", N, P);
-#define SSM(NR)                                                                                                    \
-  cuca_launch(ssm_scan_kernel<NR>, dim3(H, n_seqs, (P + pb - 1) / pb), dim3(threads), (size_t)2 * tc * per * 4, stream, \
-              true, xbc, dt_raw, ld_dt, dt_col, dt_bias, a_log, d_skip, state, y, req_row0, req_count, slots, H, P, \
-              N, G, ns, tc, pb)
-  if (nr <= 4) SSM(4);
-  else if (nr <= 8) SSM(8);
-  else if (nr <= 16) SSM(16);
-  else SSM(32);
+#define SSM(NR, NST)                                                                                              \
+  cuca_launch(ssm_scan_kernel<NR, NST>, dim3(H, n_seqs, (P + pb - 1) / pb), dim3(threads), (size_t)2 * tc * per * 4, \
+              stream, true, xbc, dt_raw, ld_dt, dt_col, dt_bias, a_log, d_skip, state, y, req_row0, req_count, slots, \
+              H, P, N, G, ns, tc, pb)
+#define SSM_BY_NS(NR)                                     \
+  do {                                                    \
+    if (!exact) SSM(NR, 0);                               \
+    else if (ns == 16) SSM(NR, 16);                       \
+    else if (ns == 8) SSM(NR, 8);                         \
+    else if (ns == 4) SSM(NR, 4);                         \
+    else if (ns == 2) SSM(NR, 2);                         \
+    else SSM(NR, 1);                                      \
+  } while (0)
+  // the state divides evenly into a row count the kernels are compiled for: the form without checks
+  const bool exact = N % ns == 0 && (nr == 4 || nr == 8 || nr == 16 || nr == 32);
+  if (nr <= 4) SSM_BY_NS(4);
+  else if (nr <= 8) SSM_BY_NS(8);
+  else if (nr <= 16) SSM_BY_NS(16);
+  else SSM_BY_NS(32);
+#undef SSM_BY_NS
 #undef SSM
   CUCA_CHECK_LAUNCH("ssm_scan");
   return 0;
