@@ -461,3 +461,30 @@ def test_greedy_generation_through_the_entry_point(models, name):
         assert out.tokens == _plain_greedy(cfg, oracle.w, prompt, 12)
     stats = model.serving_stats()
     assert stats is not None
+
+
+def test_command_line_sampling_and_the_prefix_cache_refusal(models):
+    """`python -m cuca_b200` on a Bananex folder; seeded sampling is repeatable and differs from greedy somewhere;
+    the prefix cache is refused (the layers keep state that cached pages do not bring back)."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    from cuca_b200.cache.pages import StatefulCacheError
+    folder, cfg, oracle = models["once"]
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([sys.executable, "-m", "cuca_b200", "--model-dir", str(folder), "--prompt", "5 9 20 31",
+                        "--max-tokens", "6", "--temperature", "0", "--dtype", "float32"],
+                       capture_output=True, text=True, cwd=root, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == _plain_greedy(cfg, oracle.w, [5, 9, 20, 31], 6)
+    model = LocalModel.load(LocalModelConfig(source=str(folder), dtype="bfloat16", context_length=128))
+    prompt = bu.random_tokens(20, cfg["vocab"], 77)
+    a = model.generate(prompt, max_tokens=16, temperature=1.0, top_k=20, seed=5).tokens
+    b = model.generate(prompt, max_tokens=16, temperature=1.0, top_k=20, seed=5).tokens
+    c = model.generate(prompt, max_tokens=16, temperature=1.0, top_k=20, seed=6).tokens
+    assert a == b and a != c and all(0 <= t < cfg["vocab"] for t in a)
+    with pytest.raises(StatefulCacheError):
+        LocalModel.load(LocalModelConfig(source=str(folder), dtype="bfloat16", context_length=128,
+                                         batching=BatchingConfig(prefix_cache=True)))
