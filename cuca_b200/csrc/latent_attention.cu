@@ -137,6 +137,94 @@ head_linear_kernel(const float* __restrict__ a, int lda, int a_head, const TW* _
   }
 }
 
+// The same contraction on tensor cores (bfloat16 weights, many rows): tiles of 64 rows x 64 outputs, four warps of
+// 16 rows each, K in steps of 32; `a` is rounded to bfloat16 on its way into shared memory, sums are 32-bit.
+__device__ __forceinline__ void hl_ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void hl_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const float* __restrict__ a, int lda, int a_head, const __nv_bfloat16* __restrict__ w,
+                       TO* __restrict__ out, int ldo, int o_head, const float* __restrict__ gate, int ldg, int T, int N,
+                       int K) {
+  constexpr int KS = 32, RSM = KS + 8;  // rows of 80 bytes: the eight rows of an ldmatrix fall into different banks
+  __shared__ __align__(16) __nv_bfloat16 As[64 * RSM];
+  __shared__ __align__(16) __nv_bfloat16 Ws[64 * RSM];
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.z, t0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+  const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  const float* ah = a + (size_t)h * a_head;
+  for (int k0 = 0; k0 < K; k0 += KS) {
+    float av[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {  // 64 rows x 32 values, a row's 32 values side by side over a warp
+      const int e = threadIdx.x + i * 128, r = e >> 5, kk = e & 31;
+      av[i] = (t0 + r < T && k0 + kk < K) ? ah[(size_t)(t0 + r) * lda + k0 + kk] : 0.f;
+    }
+    __nv_bfloat16 wv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = threadIdx.x + i * 128, r = e >> 5, kk = e & 31;
+      wv[i] = (n0 + r < N && k0 + kk < K) ? wh[(size_t)(n0 + r) * K + k0 + kk] : __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();  // the step before is read to the end
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = threadIdx.x + i * 128, r = e >> 5, kk = e & 31;
+      As[r * RSM + kk] = __float2bfloat16_rn(av[i]);
+      Ws[r * RSM + kk] = wv[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KS; kk += 16) {
+      uint32_t af[4];
+      hl_ldsm_x4(af, As + (warp * 16 + a_row) * RSM + kk + a_col);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bf[4];
+        hl_ldsm_x4(bf, Ws + (np * 16 + b_row) * RSM + kk + b_col);
+        hl_mma(acc[2 * np], af, bf[0], bf[1]);
+        hl_mma(acc[2 * np + 1], af, bf[2], bf[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = t0 + warp * 16 + g + 8 * i;
+    if (row >= T) continue;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + nt * 8 + 2 * t + j;
+        if (n >= N) continue;
+        float v = acc[nt][2 * i + j];
+        if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)row * ldg + (size_t)h * N + n]));
+        out[(size_t)row * ldo + (size_t)h * o_head + n] = from_f32<TO>(v);
+      }
+  }
+}
+
 // The same contraction for up to 16 rows (single decoded tokens): a warp per (head, output) reads its weight row once
 // and keeps a sum per row; the lanes split K. Used in the serving precision only: its sums run in another order
 // than the tiled kernel's.
@@ -298,6 +386,18 @@ CUCA_API int cuca_head_linear(const float* a, int lda, int a_head, const void* w
   }
   dim3 grid((N + 63) / 64, (T + 63) / 64, H);
   CUCA_REQUIRE(grid.y <= 65535, "head_linear: %d rows exceed the launch limit", T);
+  if (w_dtype == CUCA_BF16) {
+    if (out_dtype == CUCA_F32)
+      cuca_launch(head_linear_mma_kernel<float>, grid, dim3(128), 0, stream, true, a, lda, a_head,
+                  (const __nv_bfloat16*)w, (float*)out, ldo, o_head, gate, ldg, T, N, K);
+    else if (out_dtype == CUCA_BF16)
+      cuca_launch(head_linear_mma_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, true, a, lda, a_head,
+                  (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ldo, o_head, gate, ldg, T, N, K);
+    else
+      CUCA_REQUIRE(false, "head_linear: unsupported dtypes %d/%d", w_dtype, out_dtype);
+    CUCA_CHECK_LAUNCH("head_linear");
+    return 0;
+  }
 #define HL(TW, TO)                                                                                               \
   cuca_launch(head_linear_kernel<TW, TO>, grid, dim3(256), 0, stream, true, a, lda, a_head, (const TW*)w, (TO*)out, \
               ldo, o_head, gate, ldg, T, N, K)
