@@ -1,8 +1,6 @@
 """Bananex on the GPU against the plain implementation (`plain_bananex.py`): every mechanism alone, whole and cut,
 then whole models through the replayer in the four work splits, pages and slots used again, long decoding past
 every window, and greedy generation through the entry point and its scheduler."""
-import json
-
 import numpy as np
 import pytest
 import torch
@@ -14,15 +12,10 @@ import replay_util as ru
 pytestmark = pytest.mark.gpu
 
 
-
 @pytest.fixture(scope="module")
 def rt32():
     from cuca_b200.runtime import Runtime
     return Runtime("cuda:0", torch.float32)
-
-
-def _f64(t):
-    return t.detach().cpu().to(torch.float64).numpy()
 
 
 def _step(dev, portions, slots):
@@ -128,7 +121,7 @@ def _part(kind, cls, layer, rt, E, eps, prefix="l0.mix."):
     return cls(spec, rt)
 
 
-def _weights_for(part, seed, scale=None):
+def _weights_for(part, seed):
     rs = np.random.default_rng(seed)
     ws = {}
     for name, need in part.tensors().items():
