@@ -63,7 +63,7 @@ norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ gain, i
   const float* xr = x + (size_t)r0 * E;
   const float* xl = x + (size_t)(r0 + n - 1) * E;
   const float ir = rsqrtf(row_sumsq(xr, E, red) / (float)E + eps);
-  const float il = rsqrtf(row_sumsq(xl, E, red) / (float)E + eps);
+  const float il = n == 1 ? ir : rsqrtf(row_sumsq(xl, E, red) / (float)E + eps);  // a single token: the same row
   for (int i = threadIdx.x; i < E; i += NT) {
     const float g = gain[i * gain_stride];
     out[(size_t)r0 * E + i] = from_f32<TO>(shifted(normed(xr[i], ir, g), keep[i], mix[i]));
