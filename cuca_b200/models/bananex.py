@@ -65,11 +65,12 @@ def bananex_spec(cfg: BananexConfig) -> ModelSpec:
                                 mixer=_mixer_spec(layer, E, eps, p + "mix."), mixer_norm=norm(p + "norm1"),
                                 feed_forward=ff, ffn_norm=ffn_norm))
     schedule, stream_ops = [], []
-    if cfg.loop is not None:
+    looped = cfg.loop is not None and cfg.loop.stop > cfg.loop.start
+    if looped:
         stream_ops.append(PartSpec("loop_entry", {"width": E, "times": cfg.loop.times},
                                    {"mix": "loop.in", "step": "loop.step"}))
     for n, (i, t) in enumerate(cfg.run_order()):
-        if t is not None and i == cfg.loop.start:
+        if looped and t is not None and i == cfg.loop.start:
             schedule.append(Between(op=0, arg=t))
         schedule.append(Run(layer=i, cache=n, owns=True))
     # a layer without feed-forward has no use for the norms around one, should a file carry them
@@ -79,7 +80,9 @@ def bananex_spec(cfg: BananexConfig) -> ModelSpec:
         embedding=PartSpec("embedding", {"vocab": cfg.vocab, "width": E}, {"weight": "embed"}),
         layers=layers, schedule=schedule, final_norm=norm("final.norm"),
         head=PartSpec("head", {"vocab": cfg.vocab, "width": E, "scale": cfg.logit_scale}, {"weight": "head"}),
-        ignorable_tensor=(lambda name: bool(spare.match(name))) if spare else (lambda name: False),
+        # ... nor has a model without a looped stretch any use for the loop's tensors
+        ignorable_tensor=lambda name: (bool(spare and spare.match(name))
+                                       or (not looped and name in ("loop.in", "loop.step"))),
         stream_ops=stream_ops)
 
 

@@ -30,6 +30,10 @@ def test_run_order_and_caches():
     assert not flat.stream_ops and all(isinstance(e, Run) for e in flat.schedule)
     once = build_spec(bu.CONFIGS["once"])  # a loop of one pass still enters through the remix
     assert isinstance(once.schedule[0], Between) and len(once.schedule) == 3
+    empty = copy.deepcopy(bu.CONFIGS["mix"])
+    empty["loop"] = {"start": 2, "stop": 2, "times": 3}  # a stretch of no layers: nothing loops, nothing is remixed
+    spec = build_spec(empty)
+    assert not spec.stream_ops and [e.layer for e in spec.schedule] == [0, 1, 2, 3] and spec.ignorable_tensor("loop.in")
     assert pb.run_order(bu.CONFIGS["mix"]) == [(0, None, False), (1, 0, True), (2, 0, False), (1, 1, True),
                                                 (2, 1, False), (3, None, False)]
 
