@@ -481,3 +481,23 @@ def test_command_line_sampling_and_the_prefix_cache_refusal(models):
     with pytest.raises(StatefulCacheError):
         LocalModel.load(LocalModelConfig(source=str(folder), dtype="bfloat16", context_length=128,
                                          batching=BatchingConfig(prefix_cache=True)))
+
+
+def test_bfloat16_generation_through_captured_graphs(models):
+    """The serving precision end to end: prompts in portions, decode steps replayed as CUDA graphs (the tensor-core
+    attention's single-token form with its key tiles dealt to several CTAs, the few-row contractions). Where two
+    logits nearly tie bfloat16 may take the other branch, so every token it takes must be a near-maximum of the
+    plain implementation's logits at its place."""
+    from cuca_b200 import BatchingConfig, LocalModel, LocalModelConfig
+    folder, cfg, oracle = models["wide"]
+    prompts = [bu.random_tokens(n, cfg["vocab"], seed=60 + n) for n in (5, 70, 33)]
+    model = LocalModel.load(LocalModelConfig(source=str(folder), dtype="bfloat16", context_length=256,
+                                             batching=BatchingConfig(max_sequences=4, prefill_chunk=32)))
+    assert model.backend.use_graphs
+    outs = model.generate(prompts, max_tokens=40, temperature=0.0)
+    assert model.backend.graph_steps > 0
+    for prompt, out in zip(prompts, outs):
+        ref = pb.forward(cfg, oracle.w, prompt + out.tokens)
+        for i, tok in enumerate(out.tokens):
+            row = ref[len(prompt) - 1 + i]
+            assert float(row.max() - row[tok]) < 0.05 * float(np.abs(row).max()), (i, tok, int(row.argmax()))
