@@ -9,12 +9,13 @@
 
 namespace {
 
-template <typename T>
+// VC: runs of 32 value columns a lane accumulates (value heads of up to 32 VC values)
+template <typename T, int VC>
 __global__ void __launch_bounds__(128)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                          const T* __restrict__ kpool, const T* __restrict__ vpool, int n_blocks, int bs,
                          const int* __restrict__ positions, const int* __restrict__ seq_of_row,
-                         const int* __restrict__ tables, int table_stride, int nh, int nkv, int d,
+                         const int* __restrict__ tables, int table_stride, int nh, int nkv, int d, int dv,
                          float scale, int window, int* err) {
   extern __shared__ float qs[];  // [4][d]
   pdl_trigger();
@@ -34,27 +35,27 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   int lo = 0;
   if (window > 0 && P - (window - 1) > 0) lo = P - (window - 1);
   float m = -INFINITY, l = 0.f;
-  float acc[8];
+  float acc[VC];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+  for (int c = 0; c < VC; ++c) acc[c] = 0.f;
   const int* table = tables + (size_t)seq * table_stride;
 
   for (int t0 = (lo / 32) * 32; t0 <= P; t0 += 32) {
     int kp = t0 + lane;
     bool valid = kp >= lo && kp <= P;
-    long long base = -1;
+    long long base = -1;  // this key's row number in the pools (key rows of d values, value rows of dv)
     if (valid) {
       int blk = table[kp / bs];
       if (blk < 0 || blk >= n_blocks) {
         if (err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
         valid = false;
       } else {
-        base = (((long long)blk * nkv + kvh) * bs + (kp % bs)) * d;
+        base = ((long long)blk * nkv + kvh) * bs + (kp % bs);
       }
     }
     float s = -INFINITY;
     if (valid) {
-      const T* kr = kpool + base;
+      const T* kr = kpool + base * d;
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot = fmaf(qv[i], to_f32(kr[i]), dot);
       s = dot * scale;
@@ -65,26 +66,26 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     float corr = expf(m - m_new);
     l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] *= corr;
+    for (int c = 0; c < VC; ++c) acc[c] *= corr;
     for (int j = 0; j < 32; ++j) {
       float pj = __shfl_sync(0xffffffffu, p, j);
       long long bj = __shfl_sync(0xffffffffu, base, j);
       if (bj < 0) continue;
-      const T* vr = vpool + bj;
+      const T* vr = vpool + bj * dv;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < VC; ++c) {
         int dim = c * 32 + lane;
-        if (dim < d) acc[c] = fmaf(pj, to_f32(vr[dim]), acc[c]);
+        if (dim < dv) acc[c] = fmaf(pj, to_f32(vr[dim]), acc[c]);
       }
     }
     m = m_new;
   }
   float inv = l > 0.f ? 1.f / l : 0.f;
-  T* o = out + (size_t)row * out_stride + (size_t)head * d;
+  T* o = out + (size_t)row * out_stride + (size_t)head * dv;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < VC; ++c) {
     int dim = c * 32 + lane;
-    if (dim < d) o[dim] = from_f32<T>(acc[c] * inv);
+    if (dim < dv) o[dim] = from_f32<T>(acc[c] * inv);
   }
 }
 
@@ -96,31 +97,129 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 CUCA_API int cuca_attention_max_head_dim() { return 256; }
 
 // q: rows of `q_stride` elements whose first nh*d hold the (rotated) query
-// heads; out: [n_rows, out_stride]; pools [n_blocks][nkv][bs][d]. Row r is at
-// position positions[r] of sequence seq_of_row[r] (< 0: padding, skipped) and
+// heads; out: [n_rows, out_stride] with nh heads of dv values; key pool [n_blocks][nkv][bs][d], value pool
+// [n_blocks][nkv][bs][dv]. Row r is at position positions[r] of sequence seq_of_row[r] (< 0: padding, skipped) and
 // sees keys max(0, P - window + 1)..P of that sequence (window 0: all).
+CUCA_API int cuca_attention_generic_v(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                      const void* kpool, const void* vpool, int n_blocks, int bs,
+                                      const int* positions, const int* seq_of_row, const int* tables,
+                                      int table_stride, int n_rows, int nh, int nkv, int d, int dv, float scale,
+                                      int window, int* err, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CUCA_REQUIRE(d > 0 && d <= cuca_attention_max_head_dim(), "attention: head size %d is outside 1..%d", d, cuca_attention_max_head_dim());
+  CUCA_REQUIRE(dv > 0 && dv <= 2 * cuca_attention_max_head_dim(), "attention: value size %d is outside 1..%d", dv,
+               2 * cuca_attention_max_head_dim());
+  CUCA_REQUIRE(nkv > 0 && nh % nkv == 0, "attention: %d query heads do not group over %d key heads", nh, nkv);
+  CUCA_REQUIRE(n_rows <= 65535, "attention: %d rows in one step exceed the launch limit 65535", n_rows);
+  dim3 grid((nh + 3) / 4, n_rows);
+  size_t smem = (size_t)4 * d * sizeof(float);
+#define AG(T, VC)                                                                                                  \
+  cuca_launch(attention_generic_kernel<T, VC>, grid, dim3(128), smem, stream, true, (const T*)q, q_stride, (T*)out, \
+              out_stride, (const T*)kpool, (const T*)vpool, n_blocks, bs, positions, seq_of_row, tables,            \
+              table_stride, nh, nkv, d, dv, scale, window, err)
+  if (dtype == CUCA_F32) {
+    if (dv <= 256) AG(float, 8); else AG(float, 16);
+  } else if (dtype == CUCA_BF16) {
+    if (dv <= 256) AG(__nv_bfloat16, 8); else AG(__nv_bfloat16, 16);
+  } else {
+    CUCA_REQUIRE(false, "attention: unknown dtype %d", dtype);
+  }
+#undef AG
+  CUCA_CHECK_LAUNCH("attention_generic");
+  return 0;
+}
+
 CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                     const void* kpool, const void* vpool, int n_blocks, int bs,
                                     const int* positions, const int* seq_of_row, const int* tables,
                                     int table_stride, int n_rows, int nh, int nkv, int d, float scale,
                                     int window, int* err, cudaStream_t stream) {
+  return cuca_attention_generic_v(q, q_stride, out, out_stride, dtype, kpool, vpool, n_blocks, bs, positions,
+                                  seq_of_row, tables, table_stride, n_rows, nh, nkv, d, d, scale, window, err, stream);
+}
+
+// ---------------------------------------------------------------- rotation and the paged write, general form
+// qkv: rows of `ld` values: nh query heads of d at column 0, nkv key heads of d at k_col, nkv value heads of dv at
+// v_col. The first `rot` values of every q and k head are rotated by the row's position, in pairs (i, i + rot/2)
+// (pairs 0) or (2i, 2i + 1) (pairs 1); q in place, k and v go to the position's page.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, const int* __restrict__ positions,
+                          const int* __restrict__ seq_of_row, const int* __restrict__ tables, int table_stride,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows, int rot,
+                          int pairs, T* __restrict__ kpool, T* __restrict__ vpool, int n_blocks, int bs, int nh,
+                          int nkv, int d, int dv, int* err) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int seq = seq_of_row[row];
+  if (seq < 0) return;
+  const int pos = positions[row];
+  const int half = rot / 2;
+  T* base = qkv + (size_t)row * ld;
+  long long page_row = -1;
+  if (nkv > 0) {
+    int blk = pos >= 0 ? tables[(size_t)seq * table_stride + pos / bs] : -1;
+    if (blk < 0 || blk >= n_blocks) {
+      if (threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_BLOCK_RANGE);
+    } else {
+      page_row = (long long)blk * nkv * bs + (pos % bs);
+    }
+  }
+  const bool in_table = pos >= 0 && pos < table_rows;
+  if (!in_table && half > 0 && threadIdx.x == 0 && err) atomicExch(err, CUCA_ERR_TOKEN_RANGE);
+  const float* cr = cos_t + (size_t)(in_table ? pos : 0) * half;
+  const float* sr = sin_t + (size_t)(in_table ? pos : 0) * half;
+  const int per_head = half + (d - rot);
+  for (int idx = threadIdx.x; idx < (nh + nkv) * per_head; idx += blockDim.x) {
+    const int head = idx / per_head, i = idx % per_head;
+    const bool is_k = head >= nh;
+    T* src = is_k ? base + k_col + (size_t)(head - nh) * d : base + (size_t)head * d;
+    T* dst = src;
+    if (is_k) {
+      if (page_row < 0) continue;
+      dst = kpool + (page_row + (long long)(head - nh) * bs) * d;
+    }
+    if (i < half) {
+      const int ia = pairs ? 2 * i : i, ib = pairs ? 2 * i + 1 : i + half;
+      const float c = in_table ? cr[i] : 1.f, sn = in_table ? sr[i] : 0.f;
+      const float a = to_f32(src[ia]), b = to_f32(src[ib]);
+      dst[ia] = from_f32<T>(a * c - b * sn);
+      dst[ib] = from_f32<T>(b * c + a * sn);
+    } else if (is_k) {
+      const int e = rot + (i - half);
+      dst[e] = src[e];
+    }
+  }
+  if (nkv > 0 && page_row >= 0) {
+    const T* vsrc = base + v_col;
+    for (int idx = threadIdx.x; idx < nkv * dv; idx += blockDim.x) {
+      const int kvh = idx / dv, e = idx % dv;
+      vpool[(page_row + (long long)kvh * bs) * dv + e] = vsrc[idx];
+    }
+  }
+}
+}  // namespace
+
+CUCA_API int cuca_rope_store_general(void* qkv, int dtype, int ld, int k_col, int v_col, const int* positions,
+                                     const int* seq_of_row, const int* tables, int table_stride, const float* cos_t,
+                                     const float* sin_t, int table_rows, int rot, int pairs, void* kpool, void* vpool,
+                                     int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv, int* err,
+                                     cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CUCA_REQUIRE(d > 0 && d <= cuca_attention_max_head_dim(), "attention: head size %d is outside 1..%d", d, cuca_attention_max_head_dim());
-  CUCA_REQUIRE(nkv > 0 && nh % nkv == 0, "attention: %d query heads do not group over %d key heads", nh, nkv);
-  CUCA_REQUIRE(n_rows <= 65535, "attention: %d rows in one step exceed the launch limit 65535", n_rows);
-  dim3 grid((nh + 3) / 4, n_rows);
-  size_t smem = (size_t)4 * d * sizeof(float);
+  CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_store: rotary size %d does not fit head size %d", rot, d);
+  CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && dv > 0, "rope_store: bad sizes");
   if (dtype == CUCA_F32)
-    cuca_launch(attention_generic_kernel<float>, grid, dim3(128), smem, stream, true, (const float*)q, q_stride,
-                (float*)out, out_stride, (const float*)kpool, (const float*)vpool, n_blocks, bs, positions,
-                seq_of_row, tables, table_stride, nh, nkv, d, scale, window, err);
+    cuca_launch(rope_store_general_kernel<float>, dim3(n_rows), dim3(256), 0, stream, true, (float*)qkv, ld, k_col,
+                v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, (float*)kpool,
+                (float*)vpool, n_blocks, bs, nh, nkv, d, dv, err);
   else if (dtype == CUCA_BF16)
-    cuca_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, true,
-                (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kpool,
-                (const __nv_bfloat16*)vpool, n_blocks, bs, positions, seq_of_row, tables, table_stride, nh, nkv, d,
-                scale, window, err);
+    cuca_launch(rope_store_general_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, true, (__nv_bfloat16*)qkv,
+                ld, k_col, v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs,
+                (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, dv, err);
   else
-    CUCA_REQUIRE(false, "attention: unknown dtype %d", dtype);
-  CUCA_CHECK_LAUNCH("attention_generic");
+    CUCA_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("rope_store_general");
   return 0;
 }

@@ -1,0 +1,213 @@
+// Several copies of the residual stream side by side (hyper-connections), X: [rows, S, E] in 32-bit:
+//   spread_streams   every copy starts as the embedding output
+//   streams_read     h = norm(sum_s r[s] X[s]) * w in the compute dtype (optionally of gathered rows)
+//   streams_write    X'[t] = sum_s M[s, t] X[s] + o[t] y for all t from the old copies, in place; optionally the next
+//                    sublayer's read of the new copies in the same launch
+//   pair_norm_add    x (+)= c (norm(a) * wa + norm(b) * wb): two sublayer outputs normed apart, then joined
+//   sigmoid_gate     a *= sigmoid(g), columns of two row-strided tensors
+// All arithmetic is 32-bit and a row's reduction order depends on the width alone, so its bits do not depend on the
+// batch it is in.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int NT = 256;
+constexpr int MAX_STREAMS = 8;
+
+__device__ __forceinline__ float block_total(float s, float* red) {
+  s = warp_sum(s);
+  __syncthreads();  // earlier readers of `red` are done
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NT / 32; ++i) tot += red[i];
+  return tot;
+}
+
+__global__ void spread_streams_kernel(const float* __restrict__ x, float* __restrict__ X, size_t n, int S, int E) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / E, e = i % E;
+    const float v = x[i];
+    for (int s = 0; s < S; ++s) X[(row * S + s) * E + e] = v;
+  }
+}
+
+// u[i] = sum_s r[s] X[row, s, i] (r null: every copy counts once)
+__device__ __forceinline__ float read_mix(const float* __restrict__ Xr, const float* rs, int S, int E, int i) {
+  float u = 0.f;
+  for (int s = 0; s < S; ++s) u = fmaf(rs ? rs[s] : 1.f, Xr[(size_t)s * E + i], u);
+  return u;
+}
+
+template <typename TO>
+__device__ __forceinline__ void read_row(const float* __restrict__ Xr, const float* rs, const float* __restrict__ w,
+                                         TO* __restrict__ out, int S, int E, float eps, float* red) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < E; i += NT) { const float u = read_mix(Xr, rs, S, E, i); ss = fmaf(u, u, ss); }
+  const float inv = 1.f / sqrtf(block_total(ss, red) / (float)E + eps);
+  for (int i = threadIdx.x; i < E; i += NT) out[i] = from_f32<TO>(read_mix(Xr, rs, S, E, i) * inv * w[i]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(NT)
+streams_read_kernel(const float* __restrict__ X, const float* __restrict__ r, const float* __restrict__ w,
+                    TO* __restrict__ out, const int* __restrict__ rows, int S, int E, float eps) {
+  __shared__ float red[NT / 32];
+  __shared__ float rs[MAX_STREAMS];
+  pdl_trigger();
+  pdl_wait();
+  if (r && threadIdx.x < S) rs[threadIdx.x] = r[threadIdx.x];
+  __syncthreads();
+  const size_t src = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  read_row<TO>(X + src * S * E, r ? rs : nullptr, w, out + (size_t)blockIdx.x * E, S, E, eps, red);
+}
+
+template <typename TO, bool NEXT>
+__global__ void __launch_bounds__(NT)
+streams_write_kernel(float* __restrict__ X, const float* __restrict__ y, const float* __restrict__ M,
+                     const float* __restrict__ o, const float* __restrict__ r2, const float* __restrict__ w2,
+                     TO* __restrict__ out2, int S, int E, float eps) {
+  __shared__ float red[NT / 32];
+  __shared__ float ms[MAX_STREAMS * MAX_STREAMS], os[MAX_STREAMS], rs[MAX_STREAMS];
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x < S * S) ms[threadIdx.x] = M[threadIdx.x];
+  if (threadIdx.x < S) {
+    os[threadIdx.x] = o[threadIdx.x];
+    rs[threadIdx.x] = NEXT ? r2[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  float* Xr = X + (size_t)blockIdx.x * S * E;
+  const float* yr = y + (size_t)blockIdx.x * E;
+  for (int i = threadIdx.x; i < E; i += NT) {
+    float old[MAX_STREAMS];
+    for (int s = 0; s < S; ++s) old[s] = Xr[(size_t)s * E + i];
+    const float yi = yr[i];
+    for (int t = 0; t < S; ++t) {
+      float v = 0.f;
+      for (int s = 0; s < S; ++s) v = fmaf(ms[s * S + t], old[s], v);
+      Xr[(size_t)t * E + i] = fmaf(os[t], yi, v);
+    }
+  }
+  if (!NEXT) return;
+  __syncthreads();  // a thread re-reads only columns it wrote itself; the barrier orders the reduction's buffer
+  read_row<TO>(Xr, rs, w2, out2 + (size_t)blockIdx.x * E, S, E, eps, red);
+}
+
+template <bool STORE>
+__global__ void __launch_bounds__(NT)
+pair_norm_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                     const float* __restrict__ wa, const float* __restrict__ wb, float c, int E, float eps) {
+  __shared__ float red[NT / 32];
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const float* ar = a + row * E;
+  const float* br = b + row * E;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < E; i += NT) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); }
+  const float ia = 1.f / sqrtf(block_total(sa, red) / (float)E + eps);
+  const float ib = 1.f / sqrtf(block_total(sb, red) / (float)E + eps);
+  for (int i = threadIdx.x; i < E; i += NT) {
+    const float v = c * (ar[i] * ia * wa[i] + br[i] * ib * wb[i]);
+    x[row * E + i] = STORE ? v : x[row * E + i] + v;
+  }
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ a, int lda, const T* __restrict__ g, int ldg, int rows, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)rows * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / n, c = i % n;
+    const float v = to_f32(a[r * lda + c]), z = to_f32(g[r * ldg + c]);
+    a[r * lda + c] = from_f32<T>(v / (1.f + expf(-z)));
+  }
+}
+
+int blocks_for(size_t n) {
+  size_t b = (n + 255) / 256;
+  return (int)(b < 1 ? 1 : (b > 4096 ? 4096 : b));
+}
+
+}  // namespace
+
+CUCA_API int cuca_streams_max() { return MAX_STREAMS; }
+
+CUCA_API int cuca_spread_streams(const float* x, float* X, int rows, int S, int E, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  CUCA_REQUIRE(S >= 1 && E >= 1, "spread_streams: bad sizes copies=%d width=%d", S, E);
+  const size_t n = (size_t)rows * E;
+  cuca_launch(spread_streams_kernel, dim3(blocks_for(n)), dim3(256), 0, stream, true, x, X, n, S, E);
+  CUCA_CHECK_LAUNCH("spread_streams");
+  return 0;
+}
+
+// out[j] = norm(sum_s r[s] X[rows ? rows[j] : j, s]) * w; r null: the plain sum of the copies
+CUCA_API int cuca_streams_read(const float* X, const float* r, const float* w, void* out, int out_dtype,
+                               const int* rows, int n_out, int S, int E, float eps, cudaStream_t stream) {
+  if (n_out == 0) return 0;
+  CUCA_REQUIRE(S >= 1 && S <= MAX_STREAMS && E >= 1, "streams_read: %d copies are outside 1..%d", S, MAX_STREAMS);
+  if (out_dtype == CUCA_F32)
+    cuca_launch(streams_read_kernel<float>, dim3(n_out), dim3(NT), 0, stream, true, X, r, w, (float*)out, rows, S, E, eps);
+  else if (out_dtype == CUCA_BF16)
+    cuca_launch(streams_read_kernel<__nv_bfloat16>, dim3(n_out), dim3(NT), 0, stream, true, X, r, w,
+                (__nv_bfloat16*)out, rows, S, E, eps);
+  else
+    CUCA_REQUIRE(false, "streams_read: unknown dtype %d", out_dtype);
+  CUCA_CHECK_LAUNCH("streams_read");
+  return 0;
+}
+
+// X'[t] = sum_s M[s * S + t] X[s] + o[t] y; with out2: out2 = norm(sum_t r2[t] X'[t]) * w2
+CUCA_API int cuca_streams_write(float* X, const float* y, const float* M, const float* o, const float* r2,
+                                const float* w2, void* out2, int out_dtype, int rows, int S, int E, float eps,
+                                cudaStream_t stream) {
+  if (rows == 0) return 0;
+  CUCA_REQUIRE(S >= 1 && S <= MAX_STREAMS && E >= 1, "streams_write: %d copies are outside 1..%d", S, MAX_STREAMS);
+  if (out2 == nullptr)
+    cuca_launch(streams_write_kernel<float, false>, dim3(rows), dim3(NT), 0, stream, true, X, y, M, o,
+                (const float*)nullptr, (const float*)nullptr, (float*)nullptr, S, E, eps);
+  else if (out_dtype == CUCA_F32)
+    cuca_launch(streams_write_kernel<float, true>, dim3(rows), dim3(NT), 0, stream, true, X, y, M, o, r2, w2,
+                (float*)out2, S, E, eps);
+  else if (out_dtype == CUCA_BF16)
+    cuca_launch(streams_write_kernel<__nv_bfloat16, true>, dim3(rows), dim3(NT), 0, stream, true, X, y, M, o, r2, w2,
+                (__nv_bfloat16*)out2, S, E, eps);
+  else
+    CUCA_REQUIRE(false, "streams_write: unknown dtype %d", out_dtype);
+  CUCA_CHECK_LAUNCH("streams_write");
+  return 0;
+}
+
+CUCA_API int cuca_pair_norm_add(float* x, const float* a, const float* b, const float* wa, const float* wb, float c,
+                                int store, int rows, int E, float eps, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (store)
+    cuca_launch(pair_norm_add_kernel<true>, dim3(rows), dim3(NT), 0, stream, true, x, a, b, wa, wb, c, E, eps);
+  else
+    cuca_launch(pair_norm_add_kernel<false>, dim3(rows), dim3(NT), 0, stream, true, x, a, b, wa, wb, c, E, eps);
+  CUCA_CHECK_LAUNCH("pair_norm_add");
+  return 0;
+}
+
+CUCA_API int cuca_sigmoid_gate(void* a, int lda, const void* g, int ldg, int dtype, int rows, int n,
+                               cudaStream_t stream) {
+  if (rows == 0 || n == 0) return 0;
+  const int blocks = blocks_for((size_t)rows * n);
+  if (dtype == CUCA_F32)
+    cuca_launch(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (float*)a, lda, (const float*)g,
+                ldg, rows, n);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (__nv_bfloat16*)a, lda,
+                (const __nv_bfloat16*)g, ldg, rows, n);
+  else
+    CUCA_REQUIRE(false, "sigmoid_gate: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("sigmoid_gate");
+  return 0;
+}

@@ -85,6 +85,23 @@ _SIGNATURES = {
     "cuca_latent_attention_mma_supported": [_I, _I],
     "cuca_latent_attention_mma": [_P, _P, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P,
                                   _P, _P],
+    "cuca_attention_generic_v": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "cuca_rope_store_general": [_P, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I,
+                                _I, _P, _P],
+    "cuca_streams_max": [],
+    "cuca_spread_streams": [_P, _P, _I, _I, _I, _P],
+    "cuca_streams_read": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P],
+    "cuca_streams_write": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "cuca_pair_norm_add": [_P, _P, _P, _P, _P, _F, _I, _I, _I, _F, _P],
+    "cuca_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
+    "cuca_matrix_state_max_dim": [],
+    "cuca_delta_scan": [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_mlstm_scan": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "cuca_head_norm_gate": [_P, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _F, _P],
+    "cuca_moe_max_experts": [],
+    "cuca_moe_route": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "cuca_moe_act_dense": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "cuca_moe_sparse": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "cuca_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, c_size_t, _P, _I, _I, _P, _P],
 }
 

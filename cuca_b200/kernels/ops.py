@@ -788,3 +788,124 @@ def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> N
         _p(qk), _p(out), _p(pool), dtype_code(pool.dtype), pool.shape[0], pool.shape[2], _p(step.positions),
         _p(step.seq_of_row), _p(cache.tables), cache.tables.shape[1], qk.shape[0], H, rank, Dk, float(scale),
         int(window or 0), _p(err), _stream()), "latent_attention")
+
+
+# ------------------------------------------------------------------ attention whose values are wider or narrower than its keys
+def rope_store_general(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, kpool, vpool,
+                       block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err) -> None:
+    """Rotate the first `rotary_dim` values of every q head (in place) and k head of `qkv` rows (q heads at column 0,
+    k heads at `k_col`, v heads of `v_head_dim` at `v_col`), pairs (i, i + n/2) or, `adjacent`, (2i, 2i + 1); write
+    k and v to the row's page."""
+    _cuda(qkv, positions, seq_of_row, kpool, vpool)
+    library.check(library.load().cuca_rope_store_general(
+        _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(positions), _p(seq_of_row),
+        _p(tables), tables.shape[1], _p(cos), _p(sin), cos.shape[0] if cos is not None else 0, int(rotary_dim),
+        int(bool(adjacent)), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads, n_kv_heads,
+        head_dim, v_head_dim, _p(err), _stream()), "rope_store_general")
+
+
+def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
+                        head_dim, v_head_dim, scale, window, err) -> None:
+    """The plain attention kernel with value heads of their own size (`vpool`: [pages, kv heads, block, v_head_dim])."""
+    _cuda(q, out, kpool, vpool)
+    library.check(library.load().cuca_attention_generic_v(
+        _p(q), int(q_stride), _p(out), out.stride(0), dtype_code(out.dtype), _p(kpool), _p(vpool), kpool.shape[0],
+        kpool.shape[2], _p(positions), _p(seq_of_row), _p(tables), tables.shape[1], out.shape[0], n_heads,
+        n_kv_heads, head_dim, v_head_dim, float(scale), int(window or 0), _p(err), _stream()), "attention_generic")
+
+
+def sigmoid_gate_(a, gate) -> None:
+    """a *= sigmoid(gate); both [rows, n] of one dtype, rows of any stride."""
+    _cuda(a, gate)
+    library.check(library.load().cuca_sigmoid_gate(_p(a), a.stride(0), _p(gate), gate.stride(0), dtype_code(a.dtype),
+                                                   a.shape[0], a.shape[1], _stream()), "sigmoid_gate")
+
+
+# ------------------------------------------------------------------ several copies of the residual stream
+STREAMS_MAX = 8  # `cuca_streams_max` says the same
+
+
+def spread_streams(x, X, copies: int) -> None:
+    """X[r, s] = x[r] for every copy s; x: [rows, E], X: [rows, copies * E], both 32-bit."""
+    _cuda(x, X)
+    library.check(library.load().cuca_spread_streams(_p(x), _p(X), x.shape[0], int(copies), x.shape[1], _stream()),
+                  "spread_streams")
+
+
+def streams_read(X, read, weight, out, copies: int, eps: float, rows=None) -> None:
+    """out = RMSNorm(sum_s read[s] X[:, s]) * weight (read None: the plain sum); `rows` gathers rows of X."""
+    _cuda(X, read, weight, out, rows)
+    library.check(library.load().cuca_streams_read(_p(X), _p(read), _p(weight), _p(out), dtype_code(out.dtype),
+                                                   _p(rows), out.shape[0], int(copies), out.shape[1], float(eps),
+                                                   _stream()), "streams_read")
+
+
+def streams_write(X, y, mix, write, copies: int, eps: float, read2=None, weight2=None, out2=None) -> None:
+    """X[:, t] <- sum_s mix[s, t] X[:, s] + write[t] y, all copies from the old ones; with `out2` also
+    out2 = RMSNorm(sum_t read2[t] X[:, t]) * weight2 of the new copies."""
+    _cuda(X, y, mix, write, read2, weight2, out2)
+    library.check(library.load().cuca_streams_write(
+        _p(X), _p(y), _p(mix), _p(write), _p(read2), _p(weight2), _p(out2),
+        dtype_code(out2.dtype) if out2 is not None else 0, y.shape[0], int(copies), y.shape[1], float(eps), _stream()),
+        "streams_write")
+
+
+def pair_norm_add(x, a, b, wa, wb, c: float, eps: float, store: bool = False) -> None:
+    """x += c (RMSNorm(a) * wa + RMSNorm(b) * wb), or x = ... with `store`; all 32-bit [rows, E]."""
+    _cuda(x, a, b, wa, wb)
+    library.check(library.load().cuca_pair_norm_add(_p(x), _p(a), _p(b), _p(wa), _p(wb), float(c), int(bool(store)),
+                                                    x.shape[0], x.shape[1], float(eps), _stream()), "pair_norm_add")
+
+
+# ------------------------------------------------------------------ mixers with a matrix state per head
+MATRIX_STATE_MAX_DIM = 1024  # `cuca_matrix_state_max_dim` says the same
+
+
+def delta_scan(qkv, a_raw, dt_bias, a_log, b_src, b_col, state, out, step, H, G, d, dv) -> None:
+    """The delta rule with a decay per key channel along every request's rows (see `parts/recurrent.py:GatedDelta`)."""
+    _cuda(qkv, a_raw, dt_bias, a_log, b_src, state, out)
+    library.check(library.load().cuca_delta_scan(
+        _p(qkv), qkv.stride(0), _p(a_raw), _p(dt_bias), _p(a_log), _p(b_src), b_src.stride(0), int(b_col), _p(state),
+        _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots), step.n_seqs, H, G, d, dv, _stream()),
+        "delta_scan")
+
+
+def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem, nrm, mx, out, step, H, d, dv) -> None:
+    _cuda(proj, mem, nrm, mx, out)
+    library.check(library.load().cuca_mlstm_scan(
+        _p(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(i_col), int(f_col), _p(i_bias), _p(f_bias),
+        float(cap), _p(mem), _p(nrm), _p(mx), _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots),
+        step.n_seqs, H, d, dv, _stream()), "mlstm_scan")
+
+
+def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:
+    """out[r, h] = o[r, h] / rms(o[r, h]) * weight * sigmoid(gate[r, h]); weight [dv] for every head or [H dv]."""
+    _cuda(o, weight, gate, out)
+    library.check(library.load().cuca_head_norm_gate(
+        _p(o), _p(weight), dv if per_head else 0, _p(gate), dtype_code(gate.dtype) if gate is not None else 0,
+        gate.stride(0) if gate is not None else 0, _p(out), dtype_code(out.dtype), o.shape[0], H, dv, float(eps),
+        _stream()), "head_norm_gate")
+
+
+# ------------------------------------------------------------------ routed feed-forward
+MOE_MAX_EXPERTS, MOE_MAX_TOP = 1024, 32
+
+
+def moe_route(logits, top, idx, wts, dense=None) -> None:
+    _cuda(logits, idx, wts, dense)
+    library.check(library.load().cuca_moe_route(_p(logits), logits.shape[0], logits.shape[1], int(top), _p(idx),
+                                                _p(wts), _p(dense), _stream()), "moe_route")
+
+
+def moe_act_dense(u, dense, a, E, F) -> None:
+    _cuda(u, dense, a)
+    library.check(library.load().cuca_moe_act_dense(_p(u), _p(dense), _p(a), dtype_code(u.dtype), u.shape[0], E, F,
+                                                    _stream()), "moe_act_dense")
+
+
+def moe_sparse(h, w_up, w_down, idx, wts, a, y, store, top, E, F) -> None:
+    """y (+)= sum over a token's chosen experts of weight * down_e(relu(up_e h)^2), reading only those experts."""
+    _cuda(h, w_up, w_down, idx, wts, a, y)
+    library.check(library.load().cuca_moe_sparse(_p(h), _p(w_up), _p(w_down), _p(idx), _p(wts), _p(a), _p(y),
+                                                 int(bool(store)), dtype_code(h.dtype), h.shape[0], int(top), E, F,
+                                                 h.shape[1], y.shape[1], _stream()), "moe_sparse")

@@ -3,7 +3,8 @@ from __future__ import annotations
 
 import torch
 
-from ..parts import (attention, block, embedding, latent_attention, mlp, norm, recurrent, rope,  # noqa: F401
+from ..kernels import ops
+from ..parts import (attention, block, embedding, latent_attention, mlp, norm, parallel, recurrent, rope,  # noqa: F401
                      stream_ops)  # (register the built-in parts)
 from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, STREAM_OPS, TensorNeed
 from ..parts.embedding import OutputHead, TokenEmbedding
@@ -31,6 +32,7 @@ class Model:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, runtime)
         self.head = OutputHead(spec.head, runtime)
         self.loaded = False
+        self.layer_hook = None  # called as (number of the layer run, ResidualStream) after every layer run
 
     # ------------------------------------------------------------ description
     def parts(self):
@@ -101,16 +103,25 @@ class Model:
         """Run the step's rows through the model; logits [wanted rows, vocab] in 32-bit, or None."""
         x = torch.empty(step.n_rows, self.spec.width, dtype=torch.float32, device=self.rt.device)
         self.embedding.forward(step.tokens, x)
+        if self.spec.streams is not None:  # every copy of the stream starts as the embedding output
+            wide = torch.empty(step.n_rows, self.spec.streams * self.spec.width, dtype=torch.float32,
+                               device=self.rt.device)
+            ops.spread_streams(x, wide, self.spec.streams)
+            x = wide
         stream = self.rt.stream(x)
         origin = None
         if self.stream_ops:  # they read the embedding output, which the layers overwrite in place
             origin = torch.empty_like(x)
             self.embedding.forward(step.tokens, origin)
+        n_run = 0
         for run in self.spec.schedule:
             if isinstance(run, Between):
                 self.stream_ops[run.op].forward(stream, origin, step, run.arg)
             else:
                 self.blocks[run.layer].forward(stream, step, cache.view(run.cache, step))
+                if self.layer_hook is not None:
+                    self.layer_hook(n_run, stream)
+                n_run += 1
         if step.logit_rows is None or step.n_logit_rows == 0:
             stream.drop_pending()
             return None

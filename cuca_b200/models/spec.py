@@ -56,6 +56,7 @@ class ModelSpec:
     eos_token_ids: tuple = ()
     ignorable_tensor: Callable[[str], bool] = field(default=lambda name: False)
     stream_ops: list = field(default_factory=list)  # PartSpecs of what `Between` entries of the schedule name
+    streams: Optional[int] = None  # copies of the residual stream the blocks carry side by side (None: the one stream)
 
     def runs(self):
         """The schedule's layer runs, without what happens between them."""

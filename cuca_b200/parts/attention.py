@@ -10,6 +10,11 @@ projections are stacked into one weight at load (the reference accepts the
 stacked form: model/cpu.rs:3296-3301).
 
 A layer that reads another layer's pages (`shares_cache`) has only q and o.
+
+Values may have a size of their own (`v_head_dim`), the concatenated heads may pass an output gate
+sigmoid(W_g h) before the output projection (`gate`), and the rotation may pair adjacent dimensions: any of these
+takes the general path (one stacked projection q | k | v | gate, a rotate-and-store kernel that knows the columns,
+the plain attention kernel with value rows of their own size).
 """
 from __future__ import annotations
 
@@ -24,8 +29,8 @@ from .base import POSITIONS, CacheNeeds, KvNeeds, Mixer, PartSpec, TensorNeed, r
 @register_mixer("attention")
 class PagedAttention(Mixer):
     """params: width, n_heads, n_kv_heads, head_dim, window (None: all keys), scale (None: 1/sqrt(head_dim)),
-    position (PartSpec or None), shares_cache (bool). tensors: q, k, v, o and optional q_bias, k_bias,
-    v_bias, o_bias."""
+    position (PartSpec or None), shares_cache (bool), v_head_dim (None: head_dim), gate (bool). tensors: q, k, v, o,
+    g (with `gate`) and optional q_bias, k_bias, v_bias, o_bias."""
 
     graph_safe = True
 
@@ -39,6 +44,8 @@ class PagedAttention(Mixer):
         self.window = p.get("window")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
         self.shares_cache = bool(p.get("shares_cache", False))
+        self.v_head_dim = int(p["v_head_dim"]) if p.get("v_head_dim") else self.head_dim
+        self.gated = bool(p.get("gate", False))
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_kv_heads} key heads must divide {self.n_heads} query heads")
         if not 1 <= self.head_dim <= ops.ATTENTION_MAX_HEAD_DIM:
@@ -47,18 +54,30 @@ class PagedAttention(Mixer):
         pos = p.get("position")
         self.position = POSITIONS.get(pos.kind)(pos, runtime) if isinstance(pos, PartSpec) else None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+        # what the stacked-projection kernels of the usual path do not take
+        self.general = (self.v_head_dim != self.head_dim or self.gated
+                        or getattr(self.position, "pairs", "half") != "half")
+        if self.general and self.shares_cache:
+            raise ValueError("attention: a layer that reads another layer's pages takes neither a value size of its "
+                             "own, an output gate nor adjacent rotation pairs")
+        if self.general and not 1 <= self.v_head_dim <= 2 * ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError(f"attention: value size {self.v_head_dim} is outside what the kernels take "
+                             f"(1..{2 * ops.ATTENTION_MAX_HEAD_DIM})")
 
     # ------------------------------------------------------------ description
     def cache_needs(self):
-        return CacheNeeds(kv=KvNeeds(self.n_kv_heads, self.head_dim, self.window))
+        return CacheNeeds(kv=KvNeeds(self.n_kv_heads, self.head_dim, self.window,
+                                     None if self.v_head_dim == self.head_dim else self.v_head_dim))
 
     def tensors(self):
-        t, d = self.spec.tensors, self.head_dim
+        t, d, dv = self.spec.tensors, self.head_dim, self.v_head_dim
         out = {t["q"]: TensorNeed((self.n_heads * d, self.width)),
-               t["o"]: TensorNeed((self.width, self.n_heads * d))}
+               t["o"]: TensorNeed((self.width, self.n_heads * dv))}
+        if self.gated:
+            out[t["g"]] = TensorNeed((self.n_heads * dv, self.width))
         if not self.shares_cache:
             out[t["k"]] = TensorNeed((self.n_kv_heads * d, self.width))
-            out[t["v"]] = TensorNeed((self.n_kv_heads * d, self.width))
+            out[t["v"]] = TensorNeed((self.n_kv_heads * dv, self.width))
         for role, rows in (("q_bias", self.n_heads * d), ("k_bias", self.n_kv_heads * d),
                            ("v_bias", self.n_kv_heads * d), ("o_bias", self.width)):
             if role in t and not (self.shares_cache and role in ("k_bias", "v_bias")):
@@ -67,12 +86,13 @@ class PagedAttention(Mixer):
 
     def load(self, get):
         t = self.spec.tensors
-        roles = ["q"] if self.shares_cache else ["q", "k", "v"]
+        roles = ["q"] if self.shares_cache else ["q", "k", "v"] + (["g"] if self.gated else [])
         self.w_qkv = torch.cat([get(t[r]) for r in roles], dim=0).contiguous()
         biases = [get(t[r + "_bias"]) if r + "_bias" in t else None for r in roles]
         if any(b is not None for b in biases):
-            if any(b is None for b in biases):
+            if any(b is None for b in biases[:3]):
                 raise ValueError("attention biases must be given for q, k and v together")
+            biases = [b if b is not None else biases[0].new_zeros(get(t[r]).shape[0]) for b, r in zip(biases, roles)]
             self.b_qkv = torch.cat(biases).contiguous()
         self.w_o = get(t["o"])
         self.b_o = get(t["o_bias"]) if "o_bias" in t else None
@@ -91,8 +111,25 @@ class PagedAttention(Mixer):
         (`StepBatch.req_row0/req_count/req_start`) and shared by the attention layers of the step."""
         return ops.attention_plan(step)
 
+    def forward_general(self, h, stream, step, cache) -> None:
+        """q | k | v | gate in one projection; rotation (either pairing, part of a head) and the page write; the plain
+        attention kernel over value rows of their own size; the gate; the output projection."""
+        nh, nkv, d, dv = self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim
+        proj = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)
+        cos, sin, rot, adjacent = self.position.tables() if self.position is not None else (None, None, 0, False)
+        ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
+                               rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err)
+        attn = self.rt.empty(h.shape[0], nh * dv)
+        ops.attention_generic_v(proj, proj.stride(0), attn, cache.k, cache.v, step.positions, step.seq_of_row,
+                                cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err)
+        if self.gated:
+            ops.sigmoid_gate_(attn, proj[:, (nh + nkv) * d + nkv * dv:])
+        stream.add_linear(attn, self.w_o, bias=self.b_o)
+
     def forward(self, h, stream, step, cache) -> None:
         stream = self.rt.stream(stream)
+        if self.general:
+            return self.forward_general(h, stream, step, cache)
         nh, d = self.n_heads, self.head_dim
         nkv = 0 if self.shares_cache else self.n_kv_heads
         fused = self.position.fused_tables() if self.position is not None else None

@@ -45,6 +45,7 @@ class TensorNeed:
     optional: bool = False
     keep_fp32: bool = False  # small vectors (norm weights) stay 32-bit in every mode
     init: str = "normal"  # random-weights mode: "normal" N(0, std) or "ones"
+    free: tuple = ()  # axes whose size the file decides (a size no configuration key gives); `shape` holds what random weights get
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 """Block arrangements. `pre_norm`: x += mixer(norm(x)); x += ffn(norm(x))
 (src/provider/local/model/cpu.rs:2650-2704 with pre_norms on, post_norms off).
 `sandwich_shift`: a norm before and after each sublayer, and the mixer reads its input mixed with the previous
-token's: x += n1b(mixer(shift(n1(x)))); x += n2b(ffn(n2(x)))."""
+token's: x += n1b(mixer(shift(n1(x)))); x += n2b(ffn(n2(x))).
+`hyper_connections`: several copies of the stream; a sublayer reads a weighted sum of them and writes into all."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -81,3 +82,63 @@ class SandwichShiftBlock(Block):
         y = ResidualStream.unwritten(rt, rows, self.width)
         self.feed_forward.forward(f, y, step)
         ops.post_norm_add(x, y.data, self.post2, self.eps)
+
+
+@register_block("hyper_connections")
+class HyperConnectionsBlock(Block):
+    """The stream is `streams` copies X[0..s-1] side by side (`[rows, s * width]`). Sublayer c (1: mixer, 2:
+    feed-forward) has a read vector r [s], a write vector o [s] and a matrix M [s, s] (rows: from, columns: to):
+        y = sublayer(norm_c(sum_a r[a] X[a]));   X'[b] = sum_a M[a, b] X[a] + o[b] y   for every b, from the old copies.
+    The norms are the layer's `mixer_norm` / `ffn_norm` parts (their weights are used by this block's kernels, which
+    read the copies, norm and round in one pass). Three passes over the copies per layer: the mixer's read; the
+    mixer's write with the feed-forward's read of the new copies; the feed-forward's write.
+
+    params: width, streams, eps. tensors: read1, write1, mix1 and, with a feed-forward, read2, write2, mix2."""
+
+    def __init__(self, spec, runtime, mixer, feed_forward, mixer_norm, ffn_norm):
+        super().__init__(spec, runtime, mixer, feed_forward, mixer_norm, ffn_norm)
+        self.width = int(spec.params["width"])
+        self.streams = int(spec.params["streams"])
+        self.eps = float(spec.params["eps"])
+        if not 1 <= self.streams <= ops.STREAMS_MAX:
+            raise ValueError(f"hyper-connections: {self.streams} copies of the stream are outside 1..{ops.STREAMS_MAX}")
+        self.hc = {}
+
+    def _subs(self):
+        return ("1",) if self.feed_forward is None else ("1", "2")
+
+    def tensors(self):
+        t, s = self.spec.tensors, self.streams
+        out = {}
+        for c in self._subs():
+            out[t["read" + c]] = TensorNeed((s,), keep_fp32=True)
+            out[t["write" + c]] = TensorNeed((s,), keep_fp32=True)
+            out[t["mix" + c]] = TensorNeed((s, s), keep_fp32=True)
+        return out
+
+    def load(self, get):
+        t = self.spec.tensors
+        for c in self._subs():
+            self.hc[c] = tuple(get(t[k + c]) for k in ("read", "write", "mix"))
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for ws in self.hc.values() for w in ws)
+
+    def forward(self, stream, step, cache) -> None:
+        rt, S, E = self.rt, self.streams, self.width
+        X = rt.stream(stream).data
+        rows = X.shape[0]
+        read1, write1, mix1 = self.hc["1"]
+        h = rt.empty(rows, E)
+        ops.streams_read(X, read1, self.mixer_norm.weight, h, S, self.mixer_norm.eps)
+        y = ResidualStream.unwritten(rt, rows, E)
+        self.mixer.forward(h, y, step, cache)
+        if self.feed_forward is None:
+            ops.streams_write(X, y.data, mix1, write1, S, self.eps)
+            return
+        read2, write2, mix2 = self.hc["2"]
+        f = rt.empty(rows, E)
+        ops.streams_write(X, y.data, mix1, write1, S, self.eps, read2=read2, weight2=self.ffn_norm.weight, out2=f)
+        y = ResidualStream.unwritten(rt, rows, E)
+        self.feed_forward.forward(f, y, step)
+        ops.streams_write(X, y.data, mix2, write2, S, self.eps)

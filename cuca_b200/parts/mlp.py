@@ -80,3 +80,68 @@ class DenseActivation(FeedForward):
         a = self.rt.linear(h, self.w_up, bias=self.b_up)
         ops.gelu_(a, tanh_form=self.act == "gelu_tanh")
         self.rt.stream(stream).add_linear(a, self.w_down, bias=self.b_down)
+
+
+@register_feed_forward("routed")
+class RoutedExperts(FeedForward):
+    """Every token goes to the `top` of `experts` small feed-forwards with the largest router logits z = W_r f
+    (32-bit), weighted by the softmax over the chosen logits alone: y = sum_e p_e down_e(act(up_e f)), act the
+    square of relu. The experts' weights are stacked at load (`up` [experts * inner, width], `down` [width,
+    experts * inner]). Many tokens: all experts' up-projections in one contraction, the activation weighted per
+    expert (0 for the ones a token did not choose), one contraction over (expert, inner) down. Few tokens: only the
+    chosen experts' rows are read, a warp per output. Both sum a token's experts in a fixed order.
+
+    params: width, inner, experts, top, act ("relu2"). tensors: router [experts, width], `up{e}` [inner, width] and
+    `down{e}` [width, inner] for every expert e."""
+
+    graph_safe = True
+    SPARSE_MAX_TOKENS = 32  # up to this many tokens only the chosen experts are read
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width, self.inner = int(p["width"]), int(p["inner"])
+        self.experts, self.top = int(p["experts"]), int(p["top"])
+        if str(p.get("act", "relu2")) != "relu2":
+            raise ValueError(f"routed feed-forward: activation `{p.get('act')}` is unknown; known: relu2")
+        if not 1 <= self.top <= min(self.experts, ops.MOE_MAX_TOP) or self.experts > ops.MOE_MAX_EXPERTS:
+            raise ValueError(f"routed feed-forward: {self.top} of {self.experts} experts is outside what the kernels "
+                             f"take (experts <= {ops.MOE_MAX_EXPERTS}, chosen <= {ops.MOE_MAX_TOP})")
+        self.w_router = self.w_up = self.w_down = None
+
+    def tensors(self):
+        t = self.spec.tensors
+        out = {t["router"]: TensorNeed((self.experts, self.width))}
+        for e in range(self.experts):
+            out[t[f"up{e}"]] = TensorNeed((self.inner, self.width))
+            out[t[f"down{e}"]] = TensorNeed((self.width, self.inner))
+        return out
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_router = get(t["router"])
+        self.w_up = torch.cat([get(t[f"up{e}"]) for e in range(self.experts)], dim=0).contiguous()
+        self.w_down = torch.cat([get(t[f"down{e}"]) for e in range(self.experts)], dim=1).contiguous()
+
+    def weight_bytes(self):
+        """What a token's step reads: the router and the chosen experts."""
+        per = self.w_up.element_size() * 2 * self.inner * self.width
+        return self.w_router.numel() * self.w_router.element_size() + self.top * per
+
+    def forward(self, h, stream, step) -> None:
+        rt, T = self.rt, h.shape[0]
+        logits = rt.linear(h, self.w_router, out_dtype=torch.float32)
+        idx = torch.empty(T, self.top, dtype=torch.int32, device=rt.device)
+        wts = torch.empty(T, self.top, dtype=torch.float32, device=rt.device)
+        if T <= self.SPARSE_MAX_TOKENS:
+            ops.moe_route(logits, self.top, idx, wts)
+            a = rt.empty(T * self.top, self.inner)
+            y, fresh = rt.stream(stream).claim()
+            ops.moe_sparse(h, self.w_up, self.w_down, idx, wts, a, y, fresh, self.top, self.experts, self.inner)
+            return
+        spread = torch.empty(T, self.experts, dtype=torch.float32, device=rt.device)
+        ops.moe_route(logits, self.top, idx, wts, spread)
+        u = rt.linear(h, self.w_up)
+        a = torch.empty_like(u)
+        ops.moe_act_dense(u, spread, a, self.experts, self.inner)
+        rt.stream(stream).add_linear(a, self.w_down)

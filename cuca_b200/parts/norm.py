@@ -54,3 +54,20 @@ class ScalarRMSNorm(RMSNorm):
 
     def weight_bytes(self):
         return self.gain.element_size()
+
+
+@register_norm("rmsnorm_streams")
+class StreamsRMSNorm(RMSNorm):
+    """RMSNorm of the sum of the stream's copies: h = n(sum_s X[:, s]) * w, for a stream `[rows, streams * width]`.
+    params: width, eps, streams. tensors: weight [width]."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.streams = int(spec.params["streams"])
+
+    def forward(self, stream, rows=None):
+        X = self.rt.stream(stream).data
+        n = X.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.empty(n, self.width)
+        ops.streams_read(X, None, self.weight, out, self.streams, self.eps, rows)
+        return out

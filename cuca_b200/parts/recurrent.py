@@ -118,3 +118,151 @@ class Mamba2(Mixer):
         out = rt.empty(rows, self.inner)
         ops.gated_group_norm(y, proj, self.norm_w, out, self.norm_groups, self.eps)
         rt.stream(stream).add_linear(out, self.w_o)
+
+
+@register_mixer("gated_delta")
+class GatedDelta(Mixer):
+    """The delta rule with a gate on the write and a decay per head and key channel. q, k (`kv_heads` heads of
+    `dim`) and v (`heads` heads of `vdim`) pass a short causal convolution per channel (no bias) and silu; q and k
+    become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q times dim^(-1/2); head a reads q/k head
+    a // (heads / kv_heads). beta = sigmoid(W_b h) per head;
+    g = exp(-exp(A_log[a]) * softplus(W_a2 (W_a1 h) + dt_bias)) per head and key channel. Per head, S of dim x vdim:
+        S <- g[:, None] * S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees the write).
+    o / rms(o) per head, times `norm` [vdim], times sigmoid(W_g2 (W_g1 h)), then W_o. The ranks of the two low-rank
+    pairs are the stored tensors' (`decay_rank`, `gate_rank` only size random weights).
+    The state is S (32-bit) and the convolution's last taps - 1 inputs.
+    params: width, heads, kv_heads, dim, vdim, conv (taps), eps, decay_rank, gate_rank.
+    tensors: q, k, v, q_conv, k_conv, v_conv, b, A_log, dt_bias, a1, a2, g1, g2, norm, o."""
+
+    graph_safe = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width = int(p["width"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p.get("kv_heads") or p["heads"])
+        self.dim, self.vdim, self.taps = int(p["dim"]), int(p["vdim"]), int(p["conv"])
+        self.eps = float(p["eps"])
+        self.decay_rank = int(p.get("decay_rank") or max(8, self.dim // 4))
+        self.gate_rank = int(p.get("gate_rank") or max(8, self.vdim // 4))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"gated_delta: {self.kv_heads} key heads must divide {self.heads} heads")
+        if self.taps < 1:
+            raise ValueError("gated_delta: the convolution needs at least one tap")
+        if self.dim > ops.MATRIX_STATE_MAX_DIM:
+            raise ValueError(f"gated_delta: {self.dim} key channels exceed {ops.MATRIX_STATE_MAX_DIM}")
+        self.qk = self.kv_heads * self.dim
+        self.channels = 2 * self.qk + self.heads * self.vdim
+        self.w_in = self.w_low = self.w_a2 = self.w_g2 = self.conv_w = self.dt_bias = self.a_log = None
+        self.norm_w = self.w_o = None
+
+    def cache_needs(self):
+        return CacheNeeds(state={"conv": StateNeeds((self.taps - 1, self.channels)),
+                                 "delta": StateNeeds((self.heads, self.vdim, self.dim))})
+
+    def tensors(self):
+        t, E, H = self.spec.tensors, self.width, self.heads
+        inner = H * self.vdim
+        return {t["q"]: TensorNeed((self.qk, E)), t["k"]: TensorNeed((self.qk, E)), t["v"]: TensorNeed((inner, E)),
+                t["q_conv"]: TensorNeed((self.qk, self.taps)), t["k_conv"]: TensorNeed((self.qk, self.taps)),
+                t["v_conv"]: TensorNeed((inner, self.taps)), t["b"]: TensorNeed((H, E)),
+                t["A_log"]: TensorNeed((H,), keep_fp32=True), t["dt_bias"]: TensorNeed((H * self.dim,), keep_fp32=True),
+                t["a1"]: TensorNeed((self.decay_rank, E), free=(0,)),
+                t["a2"]: TensorNeed((H * self.dim, self.decay_rank), free=(1,)),
+                t["g1"]: TensorNeed((self.gate_rank, E), free=(0,)),
+                t["g2"]: TensorNeed((inner, self.gate_rank), free=(1,)),
+                t["norm"]: TensorNeed((self.vdim,), keep_fp32=True, init="ones"), t["o"]: TensorNeed((E, inner))}
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_in = torch.cat([get(t["q"]), get(t["k"]), get(t["v"]), get(t["b"])], dim=0).contiguous()
+        a1, g1 = get(t["a1"]), get(t["g1"])
+        self.w_a2, self.w_g2 = get(t["a2"]), get(t["g2"])
+        self.decay_rank, self.gate_rank = a1.shape[0], g1.shape[0]
+        if self.w_a2.shape[1] != self.decay_rank or self.w_g2.shape[1] != self.gate_rank:
+            raise ValueError(f"gated_delta: `{t['a2']}` / `{t['g2']}` do not continue `{t['a1']}` / `{t['g1']}`: ranks "
+                             f"{self.w_a2.shape[1]}, {self.w_g2.shape[1]} against {self.decay_rank}, {self.gate_rank}")
+        self.w_low = torch.cat([a1, g1], dim=0).contiguous()
+        self.conv_w = torch.cat([get(t["q_conv"]), get(t["k_conv"]), get(t["v_conv"])], dim=0).contiguous()
+        self.dt_bias, self.a_log, self.norm_w, self.w_o = get(t["dt_bias"]), get(t["A_log"]), get(t["norm"]), get(t["o"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_low, self.w_a2, self.w_g2, self.conv_w,
+                                                          self.dt_bias, self.a_log, self.norm_w, self.w_o))
+
+    def forward(self, h, stream, step, cache) -> None:
+        rt, rows = self.rt, h.shape[0]
+        H, G, d, dv, C = self.heads, self.kv_heads, self.dim, self.vdim, self.channels
+        proj = rt.linear(h, self.w_in, out_dtype=torch.float32)  # [q | k | v | b]
+        low = rt.linear(h, self.w_low)  # [a1 h | g1 h], rounded as everything is that enters a contraction
+        a_raw = rt.linear(low[:, :self.decay_rank], self.w_a2, out_dtype=torch.float32)
+        gate = rt.linear(low[:, self.decay_rank:], self.w_g2, out_dtype=torch.float32)
+        qkv = rt.empty(rows, C, dtype=torch.float32)
+        ops.causal_conv(proj, 0, self.conv_w, None, cache.state["conv"], qkv, step)
+        o = rt.empty(rows, H * dv, dtype=torch.float32)
+        ops.delta_scan(qkv, a_raw, self.dt_bias, self.a_log, proj, C, cache.state["delta"], o, step, H, G, d, dv)
+        out = rt.empty(rows, H * dv)
+        ops.head_norm_gate(o, self.norm_w, False, gate, out, H, dv, self.eps)
+        rt.stream(stream).add_linear(out, self.w_o)
+
+
+@register_mixer("mlstm")
+class MatrixLSTM(Mixer):
+    """A matrix memory with exponential gates. q = W_q h * dim^(-1/2), k = W_k h (heads x dim), v = W_v h (heads x
+    vdim); per head i = cap tanh((W_i h + b_i) / cap), f = logsigmoid(cap tanh((W_f h + b_f) / cap)); with a running
+    maximum m (0 at the start, like S and n):
+        m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n <- e^(f + m - m') n + e^(i - m') k;
+        o = S^T q / (max(|n . q|, e^(-m')) + 1e-6).
+    o / rms(o) per head, times `norm` [heads * vdim], times sigmoid(W_g h), then W_o. State: S, n, m in 32-bit.
+    params: width, heads, dim, vdim, gate_cap, eps. tensors: q, k, v, g, i, i_bias, f, f_bias, norm, o."""
+
+    graph_safe = True
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.width, self.heads = int(p["width"]), int(p["heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.cap, self.eps = float(p["gate_cap"]), float(p["eps"])
+        if self.cap <= 0:
+            raise ValueError("mlstm: gate_cap must be positive")
+        if self.dim > ops.MATRIX_STATE_MAX_DIM:
+            raise ValueError(f"mlstm: {self.dim} key channels exceed {ops.MATRIX_STATE_MAX_DIM}")
+        self.w_in = self.i_bias = self.f_bias = self.norm_w = self.w_o = None
+
+    def cache_needs(self):
+        H = self.heads
+        return CacheNeeds(state={"mem": StateNeeds((H, self.vdim, self.dim)), "norm": StateNeeds((H, self.dim)),
+                                 "max": StateNeeds((H,))})
+
+    def tensors(self):
+        t, E, H = self.spec.tensors, self.width, self.heads
+        inner = H * self.vdim
+        return {t["q"]: TensorNeed((H * self.dim, E)), t["k"]: TensorNeed((H * self.dim, E)),
+                t["v"]: TensorNeed((inner, E)), t["g"]: TensorNeed((inner, E)), t["i"]: TensorNeed((H, E)),
+                t["i_bias"]: TensorNeed((H,), keep_fp32=True), t["f"]: TensorNeed((H, E)),
+                t["f_bias"]: TensorNeed((H,), keep_fp32=True),
+                t["norm"]: TensorNeed((inner,), keep_fp32=True, init="ones"), t["o"]: TensorNeed((E, inner))}
+
+    def load(self, get):
+        t = self.spec.tensors
+        self.w_in = torch.cat([get(t[r]) for r in ("q", "k", "v", "g", "i", "f")], dim=0).contiguous()
+        self.i_bias, self.f_bias = get(t["i_bias"]), get(t["f_bias"])
+        self.norm_w, self.w_o = get(t["norm"]), get(t["o"])
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.i_bias, self.f_bias, self.norm_w, self.w_o))
+
+    def forward(self, h, stream, step, cache) -> None:
+        rt, rows = self.rt, h.shape[0]
+        H, d, dv = self.heads, self.dim, self.vdim
+        proj = rt.linear(h, self.w_in, out_dtype=torch.float32)  # [q | k | v | g | i | f]
+        k_col, v_col, g_col = H * d, 2 * H * d, 2 * H * d + H * dv
+        i_col = g_col + H * dv
+        o = rt.empty(rows, H * dv, dtype=torch.float32)
+        st = cache.state
+        ops.mlstm_scan(proj, 0, k_col, v_col, i_col, i_col + H, self.i_bias, self.f_bias, self.cap, st["mem"],
+                       st["norm"], st["max"], o, step, H, d, dv)
+        out = rt.empty(rows, H * dv)
+        ops.head_norm_gate(o, self.norm_w, True, proj[:, g_col:i_col], out, H, dv, self.eps)
+        rt.stream(stream).add_linear(out, self.w_o)

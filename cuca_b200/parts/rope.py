@@ -86,6 +86,10 @@ class RotaryEncoding(PositionEncoding):
         self.cos = cos.to(self.rt.device)
         self.sin = sin.to(self.rt.device)
 
+    def tables(self):
+        """(cos, sin, rotary_dim, adjacent) for a kernel that pairs either way."""
+        return self.cos, self.sin, self.rotary_dim, self.pairs == "adjacent"
+
     def fused_tables(self):
         if self.pairs != "half":
             raise ValueError("the fused rotate-and-store kernel pairs dimension i with i + n/2")

@@ -121,6 +121,14 @@ class ResidualStream:
         ps, self._pending = self._pending, None
         return self._tensor, ps
 
+    def claim(self):
+        """(tensor, fresh) for a kernel that adds into the stream itself: `fresh` says that the stream holds nothing
+        yet, so the kernel must store instead of add (nothing is zeroed for it)."""
+        if self._unwritten:
+            self._unwritten = False
+            return self._tensor, True
+        return self.data, False
+
     def add_linear(self, a, w, bias=None) -> None:
         """stream += a @ w.T (+ bias). Over few tokens the slices may stay pending until the next reader."""
         rt = self.rt

@@ -163,12 +163,18 @@ class RandomSource(WeightSource):
         return f"random weights (seed {self.seed}, std {self.std})"
 
 
+def _fits(need: TensorNeed, found: tuple) -> bool:
+    """Whether a stored shape is what the part expects; an axis named in `need.free` may have any size."""
+    want = tuple(need.shape)
+    return len(want) == len(found) and all(a == b or i in need.free for i, (a, b) in enumerate(zip(want, found)))
+
+
 def check_tensors(needs: dict[str, TensorNeed], shapes: dict[str, tuple],
                   ignorable: Callable[[str], bool] = lambda n: False, where: str = "") -> None:
     missing = [n for n, t in needs.items() if not t.optional and n not in shapes]
     unexpected = [n for n in shapes if n not in needs and not ignorable(n)]
     wrong = [(n, tuple(needs[n].shape), tuple(shapes[n])) for n in shapes
-             if n in needs and tuple(needs[n].shape) != tuple(shapes[n])]
+             if n in needs and not _fits(needs[n], tuple(shapes[n]))]
     if missing or unexpected or wrong:
         raise WeightsError(sorted(missing), sorted(unexpected), sorted(wrong), where)
 
