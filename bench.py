@@ -210,6 +210,24 @@ def _bananex_config(width, ff, heads, layers, vocab, window):
             "layers": [kinds[i % 3] for i in range(layers)], "loop": {"start": 0, "stop": layers // 2, "times": 2}}
 
 
+def _dupenex_config(width, ff, heads, layers, vocab, window):
+    """`layers` layers, every third one two mixers side by side (sliding-window attention with values twice as wide as
+    keys beside a matrix memory) and a routed feed-forward (eight experts of ff / 4, two chosen), the others a delta
+    rule with a decay per key channel (heads of 128 x 128) and a dense feed-forward; four copies of the stream; the
+    first half of the layers looped twice."""
+    H = max(1, width // 128)
+    delta = {"type": "channel_delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    side = {"type": "parallel",
+            "mlp": {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 8, "top": 2}},
+            "mixer": {"left": {"heads": max(2, H // 2), "kv_heads": max(1, H // 4), "dim": 128, "vdim": 256,
+                               "mask": {"size": window}, "rot": {"base": 250000.0, "dims": 64}, "scale": 128 ** -0.5},
+                      "right": {"heads": max(1, H // 4), "dim": 128, "vdim": 256, "gate_cap": 15.0}}}
+    return {"architecture": "Dupenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": 4,
+            "layers": [side if i % 3 == 1 else delta for i in range(layers)],
+            "loop": {"start": 0, "stop": layers // 2, "times": 2}}
+
+
 def _llama_config(width, ff, heads, layers, vocab):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
             "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": max(1, heads // 4),
@@ -223,7 +241,7 @@ DESIGN_SIZES = {  # name -> (width, feed-forward, heads, layers, vocabulary)
 
 
 def design_table(args) -> int:
-    """Prefill of one prompt and decode steps of `--batch` requests for the Bananex decoder and for a Llama of the
+    """Prefill of one prompt and decode steps of `--batch` requests for the chosen design and for a Llama of the
     same width, feed-forward size and number of layer runs, one JSON line per size and model: tokens/s of both
     phases, the decode step's bytes (weights once, what a request keeps) over the measured copy bandwidth."""
     import numpy as np
@@ -240,8 +258,11 @@ def design_table(args) -> int:
     for size in (args.sizes.split(",") if args.sizes else list(DESIGN_SIZES)):
         width, ff, heads, layers, vocab = DESIGN_SIZES[size]
         runs = layers + layers // 2  # the looped half runs twice
-        for name, cfg in (("bananex", _bananex_config(width, ff, heads, layers, vocab, window=1024)),
+        make = {"bananex": _bananex_config, "dupenex": _dupenex_config}[args.design]
+        for name, cfg in ((args.design, make(width, ff, heads, layers, vocab, window=1024)),
                           ("llama", _llama_config(width, ff, heads, runs, vocab))):
+            if args.only_model and name != args.only_model:
+                continue
             model = LocalModel.load(LocalModelConfig(
                 model_config=cfg, random_weights=RandomWeights(seed=3, std=0.02), dtype="bfloat16", context_length=ctx,
                 kv_block_size=16, batching=BatchingConfig(max_sequences=B, kv_tokens=B * (ctx + 64) + 2048,
@@ -325,7 +346,8 @@ def main() -> int:
                          "library's kernels beside cuBLAS (torch.matmul), cold weights; one JSON line per count")
     ap.add_argument("--decode-only", action="store_true",
                     help="with --shape llama-3.2-1b: the plain decode line at --batch instead of the mixed workload")
-    ap.add_argument("--design", default=None, choices=["bananex"],
+    ap.add_argument("--only-model", default=None, help="with --design: run only this model of the pair (the design's name or llama)")
+    ap.add_argument("--design", default=None, choices=["bananex", "dupenex"],
                     help="instead of the bench: prefill and decode of this design beside a Llama of equal width, "
                          "feed-forward size and layer runs, at --sizes (1b,3b,8b layer sizes; a few layers each)")
     ap.add_argument("--sizes", default=None, help="with --design: which of 1b,3b,8b (all else)")

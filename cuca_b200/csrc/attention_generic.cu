@@ -141,7 +141,9 @@ CUCA_API int cuca_attention_generic(const void* q, int q_stride, void* out, int 
 // ---------------------------------------------------------------- rotation and the paged write, general form
 // qkv: rows of `ld` values: nh query heads of d at column 0, nkv key heads of d at k_col, nkv value heads of dv at
 // v_col. The first `rot` values of every q and k head are rotated by the row's position, in pairs (i, i + rot/2)
-// (pairs 0) or (2i, 2i + 1) (pairs 1); q in place, k and v go to the position's page.
+// (pairs 0) or (2i, 2i + 1) (pairs 1); q in place, k and v go to the position's page. v_split r > 1: the value pool
+// is r slabs [n_blocks][nkv][bs][dv / r], slab j holding values j dv/r .. (j+1) dv/r - 1 of every head (each slab is
+// then a value pool of narrower heads for the kernels that want values as wide as keys).
 namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -149,7 +151,7 @@ rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, con
                           const int* __restrict__ seq_of_row, const int* __restrict__ tables, int table_stride,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows, int rot,
                           int pairs, T* __restrict__ kpool, T* __restrict__ vpool, int n_blocks, int bs, int nh,
-                          int nkv, int d, int dv, int* err) {
+                          int nkv, int d, int dv, int v_split, int* err) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -194,9 +196,11 @@ rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, con
   }
   if (nkv > 0 && page_row >= 0) {
     const T* vsrc = base + v_col;
+    const int ds = dv / v_split;
+    const long long slab_rows = (long long)n_blocks * nkv * bs;
     for (int idx = threadIdx.x; idx < nkv * dv; idx += blockDim.x) {
       const int kvh = idx / dv, e = idx % dv;
-      vpool[(page_row + (long long)kvh * bs) * dv + e] = vsrc[idx];
+      vpool[((e / ds) * slab_rows + page_row + (long long)kvh * bs) * ds + e % ds] = vsrc[idx];
     }
   }
 }
@@ -205,19 +209,20 @@ rope_store_general_kernel(T* __restrict__ qkv, int ld, int k_col, int v_col, con
 CUCA_API int cuca_rope_store_general(void* qkv, int dtype, int ld, int k_col, int v_col, const int* positions,
                                      const int* seq_of_row, const int* tables, int table_stride, const float* cos_t,
                                      const float* sin_t, int table_rows, int rot, int pairs, void* kpool, void* vpool,
-                                     int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv, int* err,
-                                     cudaStream_t stream) {
+                                     int n_blocks, int bs, int n_rows, int nh, int nkv, int d, int dv, int v_split,
+                                     int* err, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CUCA_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "rope_store: rotary size %d does not fit head size %d", rot, d);
   CUCA_REQUIRE(bs > 0 && nh > 0 && nkv >= 0 && d > 0 && dv > 0, "rope_store: bad sizes");
+  CUCA_REQUIRE(v_split >= 1 && dv % v_split == 0, "rope_store: %d slabs do not divide value size %d", v_split, dv);
   if (dtype == CUCA_F32)
     cuca_launch(rope_store_general_kernel<float>, dim3(n_rows), dim3(256), 0, stream, true, (float*)qkv, ld, k_col,
                 v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs, (float*)kpool,
-                (float*)vpool, n_blocks, bs, nh, nkv, d, dv, err);
+                (float*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err);
   else if (dtype == CUCA_BF16)
     cuca_launch(rope_store_general_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, true, (__nv_bfloat16*)qkv,
                 ld, k_col, v_col, positions, seq_of_row, tables, table_stride, cos_t, sin_t, table_rows, rot, pairs,
-                (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, dv, err);
+                (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, n_blocks, bs, nh, nkv, d, dv, v_split, err);
   else
     CUCA_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("rope_store_general");

@@ -130,6 +130,24 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ a, int lda, const T* __restr
   }
 }
 
+// out[r, h, j ds + e] = parts[j][r, h, e] * sigmoid(g[r, h, j ds + e]) (g null: no gate): the slabs of an attention
+// whose value heads were run as `split` narrower ones, joined again under the output gate
+template <typename T>
+__global__ void gate_merge_kernel(const T* __restrict__ parts, const T* __restrict__ g, int ldg, T* __restrict__ out,
+                                  int rows, int nh, int dv, int split) {
+  pdl_trigger();
+  pdl_wait();
+  const int ds = dv / split;
+  const size_t total = (size_t)rows * nh * dv, slab = (size_t)rows * nh * ds;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ((size_t)nh * dv);
+    const int c = (int)(i % ((size_t)nh * dv)), h = c / dv, e = c % dv;
+    float v = to_f32(parts[(e / ds) * slab + (r * nh + h) * ds + e % ds]);
+    if (g) v /= 1.f + expf(-to_f32(g[r * ldg + c]));
+    out[i] = from_f32<T>(v);
+  }
+}
+
 int blocks_for(size_t n) {
   size_t b = (n + 255) / 256;
   return (int)(b < 1 ? 1 : (b > 4096 ? 4096 : b));
@@ -209,5 +227,22 @@ CUCA_API int cuca_sigmoid_gate(void* a, int lda, const void* g, int ldg, int dty
   else
     CUCA_REQUIRE(false, "sigmoid_gate: unknown dtype %d", dtype);
   CUCA_CHECK_LAUNCH("sigmoid_gate");
+  return 0;
+}
+
+CUCA_API int cuca_gate_merge(const void* parts, const void* g, int ldg, void* out, int dtype, int rows, int nh, int dv,
+                             int split, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  CUCA_REQUIRE(split >= 1 && dv % split == 0, "gate_merge: %d slabs do not divide value size %d", split, dv);
+  const int blocks = blocks_for((size_t)rows * nh * dv);
+  if (dtype == CUCA_F32)
+    cuca_launch(gate_merge_kernel<float>, dim3(blocks), dim3(256), 0, stream, true, (const float*)parts, (const float*)g,
+                ldg, (float*)out, rows, nh, dv, split);
+  else if (dtype == CUCA_BF16)
+    cuca_launch(gate_merge_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true, (const __nv_bfloat16*)parts,
+                (const __nv_bfloat16*)g, ldg, (__nv_bfloat16*)out, rows, nh, dv, split);
+  else
+    CUCA_REQUIRE(false, "gate_merge: unknown dtype %d", dtype);
+  CUCA_CHECK_LAUNCH("gate_merge");
   return 0;
 }

@@ -87,7 +87,8 @@ _SIGNATURES = {
                                   _P, _P],
     "cuca_attention_generic_v": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "cuca_rope_store_general": [_P, _I, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I,
-                                _I, _P, _P],
+                                _I, _I, _P, _P],
+    "cuca_gate_merge": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "cuca_streams_max": [],
     "cuca_spread_streams": [_P, _P, _I, _I, _I, _P],
     "cuca_streams_read": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P],

@@ -792,16 +792,16 @@ def latent_attention(qk, out, cache, step, H, rank, Dk, scale, window, err) -> N
 
 # ------------------------------------------------------------------ attention whose values are wider or narrower than its keys
 def rope_store_general(qkv, k_col, v_col, positions, seq_of_row, tables, cos, sin, rotary_dim, adjacent, kpool, vpool,
-                       block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err) -> None:
+                       block_size, n_heads, n_kv_heads, head_dim, v_head_dim, err, v_split: int = 1) -> None:
     """Rotate the first `rotary_dim` values of every q head (in place) and k head of `qkv` rows (q heads at column 0,
     k heads at `k_col`, v heads of `v_head_dim` at `v_col`), pairs (i, i + n/2) or, `adjacent`, (2i, 2i + 1); write
-    k and v to the row's page."""
+    k and v to the row's page. `v_split` r > 1: the value pool's memory is r slabs of heads r times narrower."""
     _cuda(qkv, positions, seq_of_row, kpool, vpool)
     library.check(library.load().cuca_rope_store_general(
         _p(qkv), dtype_code(qkv.dtype), qkv.stride(0), int(k_col), int(v_col), _p(positions), _p(seq_of_row),
         _p(tables), tables.shape[1], _p(cos), _p(sin), cos.shape[0] if cos is not None else 0, int(rotary_dim),
         int(bool(adjacent)), _p(kpool), _p(vpool), kpool.shape[0], int(block_size), qkv.shape[0], n_heads, n_kv_heads,
-        head_dim, v_head_dim, _p(err), _stream()), "rope_store_general")
+        head_dim, v_head_dim, int(v_split), _p(err), _stream()), "rope_store_general")
 
 
 def attention_generic_v(q, q_stride, out, kpool, vpool, positions, seq_of_row, tables, n_heads, n_kv_heads,
@@ -819,6 +819,15 @@ def sigmoid_gate_(a, gate) -> None:
     _cuda(a, gate)
     library.check(library.load().cuca_sigmoid_gate(_p(a), a.stride(0), _p(gate), gate.stride(0), dtype_code(a.dtype),
                                                    a.shape[0], a.shape[1], _stream()), "sigmoid_gate")
+
+
+def gate_merge(parts, gate, out, n_heads, v_head_dim) -> None:
+    """out[r, h] = [parts[0][r, h] | parts[1][r, h] | ...] * sigmoid(gate[r, h]) (gate None: no gate); parts:
+    [split, rows, heads * v_head_dim / split] contiguous."""
+    _cuda(parts, gate, out)
+    library.check(library.load().cuca_gate_merge(_p(parts), _p(gate), gate.stride(0) if gate is not None else 0, _p(out),
+                                                 dtype_code(out.dtype), out.shape[0], n_heads, v_head_dim,
+                                                 parts.shape[0], _stream()), "gate_merge")
 
 
 # ------------------------------------------------------------------ several copies of the residual stream

@@ -18,6 +18,7 @@ the plain attention kernel with value rows of their own size).
 """
 from __future__ import annotations
 
+import dataclasses
 import math
 
 import torch
@@ -111,19 +112,50 @@ class PagedAttention(Mixer):
         (`StepBatch.req_row0/req_count/req_start`) and shared by the attention layers of the step."""
         return ops.attention_plan(step)
 
+    def value_split(self, cache) -> int:
+        """How this layer's value pool is laid out. r >= 1: for the tensor-core kernels, which want values as wide
+        as keys: values are r times as wide, the pool is r slabs of heads as wide as the keys, and the kernels run
+        once per slab against the same keys. 0: value rows as they are, for the plain kernel. The answer depends on
+        the layer's sizes, the compute dtype and the page size alone, so every step lays the pool out alike."""
+        d, dv, bs = self.head_dim, self.v_head_dim, cache.block_size
+        if (self.rt.dtype == torch.bfloat16 and dv % d == 0 and bs & (bs - 1) == 0
+                and ops.attention_mma_supported(self.n_heads, self.n_kv_heads, d, self.w_qkv.shape[0], self.n_heads * d)):
+            return dv // d
+        return 0
+
     def forward_general(self, h, stream, step, cache) -> None:
-        """q | k | v | gate in one projection; rotation (either pairing, part of a head) and the page write; the plain
-        attention kernel over value rows of their own size; the gate; the output projection."""
+        """q | k | v | gate in one projection; rotation (either pairing, part of a head) and the page write; attention
+        on the tensor cores, once per slab of the values, where the shape allows it, else the plain kernel over value
+        rows of their own size; the gate; the output projection."""
         nh, nkv, d, dv = self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim
+        rows = h.shape[0]
         proj = self.rt.linear(h, self.w_qkv, bias=self.b_qkv)
         cos, sin, rot, adjacent = self.position.tables() if self.position is not None else (None, None, 0, False)
+        split = self.value_split(cache)
+        plan = self.plan(step) if split else None
+        if split > 1 and plan is None:
+            raise ValueError("attention: this layer's value pool is laid out for the tensor-core kernels, which need "
+                             "the step's per-request description")
+        tensor_cores = split >= 1 and plan is not None
+        split = max(split, 1)
         ops.rope_store_general(proj, nh * d, (nh + nkv) * d, step.positions, step.seq_of_row, cache.tables, cos, sin,
-                               rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err)
-        attn = self.rt.empty(h.shape[0], nh * dv)
-        ops.attention_generic_v(proj, proj.stride(0), attn, cache.k, cache.v, step.positions, step.seq_of_row,
-                                cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err)
-        if self.gated:
-            ops.sigmoid_gate_(attn, proj[:, (nh + nkv) * d + nkv * dv:])
+                               rot, adjacent, cache.k, cache.v, cache.block_size, nh, nkv, d, dv, self.rt.err,
+                               v_split=split)
+        gate = proj[:, (nh + nkv) * d + nkv * dv:] if self.gated else None
+        attn = self.rt.empty(rows, nh * dv)
+        if tensor_cores:
+            slabs = cache.v.view(split, *cache.k.shape)
+            parts = self.rt.empty(split, rows, nh * d) if (split > 1 or gate is not None) else attn.view(1, rows, nh * d)
+            for j in range(split):
+                ops.attention(proj, parts[j], dataclasses.replace(cache, v=slabs[j]), step, plan, nh, nkv, d, self.scale,
+                              self.window, self.rt.err)
+            if parts.data_ptr() != attn.data_ptr():
+                ops.gate_merge(parts, gate, attn, nh, dv)
+        else:
+            ops.attention_generic_v(proj, proj.stride(0), attn, cache.k, cache.v, step.positions, step.seq_of_row,
+                                    cache.tables, nh, nkv, d, dv, self.scale, self.window, self.rt.err)
+            if gate is not None:
+                ops.sigmoid_gate_(attn, gate)
         stream.add_linear(attn, self.w_o, bias=self.b_o)
 
     def forward(self, h, stream, step, cache) -> None:

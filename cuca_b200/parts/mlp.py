@@ -124,9 +124,8 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.cat([get(t[f"down{e}"]) for e in range(self.experts)], dim=1).contiguous()
 
     def weight_bytes(self):
-        """What a token's step reads: the router and the chosen experts."""
-        per = self.w_up.element_size() * 2 * self.inner * self.width
-        return self.w_router.numel() * self.w_router.element_size() + self.top * per
+        """What a step of several tokens reads at most: the router and every expert once."""
+        return sum(w.numel() * w.element_size() for w in (self.w_router, self.w_up, self.w_down))
 
     def forward(self, h, stream, step) -> None:
         rt, T = self.rt, h.shape[0]

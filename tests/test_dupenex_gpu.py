@@ -196,25 +196,30 @@ def test_window_attention_alone_whole_and_cut(rt32, layer):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim, vdim", [(16, 24), (64, 128), (32, 96), (128, 128)])
 @pytest.mark.parametrize("window, far", [(None, 3), (64, 30), (17, 40), (16, 41)])
-def test_one_key_that_matters(dtype, window, far):
+def test_one_key_that_matters(dtype, window, far, dim, vdim):
     """A planted key: one unrotated dimension of q reads input column 0 and of k input column 1, both scaled up, and
     only position `far` has column 1 set, so the rows with column 0 set put nearly all their weight on that one key,
     among a hundred others, while they see it. With a window the rows just inside (distance window - 1) and just
-    outside (distance window) differ by everything; whole, decoded one by one and in portions that end between them."""
+    outside (distance window) differ by everything; whole, decoded one by one and in portions that end between them.
+    Values as wide as the keys, twice and three times as wide go through the tensor-core kernels in bfloat16 (slab
+    by slab), the other sizes and 32-bit through the plain kernel."""
     from cuca_b200.cache.device import CacheView
     from cuca_b200.runtime import Runtime
     rt = Runtime("cuda:0", dtype)
     dev, E, eps, bs, n = rt.device, 40, 1e-5, 8, 120
-    layer = du.par(heads=2, kv_heads=1, dim=16, vdim=24, window=window, dims=8, scale=0.25)
+    layer = du.par(heads=2, kv_heads=1, dim=dim, vdim=vdim, window=window, dims=8, scale=0.25)
     part = _attention(layer, rt, E, eps)
     m = layer["mixer"]["left"]
     ws = {k: du.bf16_round(v) for k, v in _weights_for(part, 13).items()}
+    for name in ("l0.mix.left.q", "l0.mix.left.k"):
+        ws[name] *= (16.0 / dim) ** 0.5  # the other scores spread by about one whatever the head size
     for head in range(2):
-        ws["l0.mix.left.q"][head * 16 + 15] = 0.0
-        ws["l0.mix.left.q"][head * 16 + 15, 0] = 8.0
-    ws["l0.mix.left.k"][15] = 0.0
-    ws["l0.mix.left.k"][15, 1] = 8.0
+        ws["l0.mix.left.q"][head * dim + dim - 1] = 0.0
+        ws["l0.mix.left.q"][head * dim + dim - 1, 0] = 8.0
+    ws["l0.mix.left.k"][dim - 1] = 0.0
+    ws["l0.mix.left.k"][dim - 1, 1] = 8.0
     needs = part.tensors()
     part.load(lambda name: torch.tensor(ws[name], dtype=torch.float32 if needs[name].keep_fp32 else dtype, device=dev))
     part.prepare(128)
@@ -230,8 +235,8 @@ def test_one_key_that_matters(dtype, window, far):
         assert np.abs(want[edge - 1] - want[edge]).max() > 0.3 * np.abs(want[edge - 1]).max()
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for cuts in ([1000], [far + 2] + [1] * 200, [min(edge, n - 3) - 1, 2, 1000], [min(edge, n - 3), 2, 1, 1, 1000]):
-        kpool = torch.zeros((20, 1, bs, 16), dtype=dtype, device=dev)
-        vpool = torch.zeros((20, 1, bs, 24), dtype=dtype, device=dev)
+        kpool = torch.zeros((20, 1, bs, dim), dtype=dtype, device=dev)
+        vpool = torch.zeros((20, 1, bs, vdim), dtype=dtype, device=dev)
         tables = torch.full((4, 16), -1, dtype=torch.int32, device=dev)
         tables[1, :15] = torch.tensor(rs.permutation(20)[:15].tolist(), dtype=torch.int32)
 
