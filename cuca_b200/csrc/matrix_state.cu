@@ -5,10 +5,12 @@
 //                     m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise from k alone;
 //                     o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
 //   head_norm_gate  out = o / rms(o) per head, times a weight, times sigmoid(gate)
-// A block takes one (head, request, run of value columns) and walks the request's rows of the step in order from the
-// state its slot holds, leaving the new state there. A value column's state rows live in the registers of NS
-// neighbouring threads (thread s holds rows s, s + NS, ...); a token's vectors are staged in shared memory a few
-// tokens at a time. The arithmetic of a token does not depend on where the sequence was cut into steps or chunks.
+// What does not depend on the state (unit vectors, decays, gates) is computed for all rows at once by a preparing
+// kernel, in place. A scan block then takes one (head, request, run of value columns) and walks the request's rows of
+// the step in order from the state its slot holds, leaving the new state there. A value column's state rows live in
+// the registers of NS neighbouring threads (thread s holds NR consecutive rows); a token's vectors are copied to
+// shared memory a few tokens ahead of their use. The arithmetic of a token does not depend on where the sequence was
+// cut into steps or chunks.
 #include "common.cuh"
 #include <math.h>
 
@@ -26,16 +28,59 @@ __device__ __forceinline__ float group_sum(float v, int NS) {
   return v;
 }
 
-// qkv: 32-bit rows of stride ld (after the short convolution and its activation): q heads at column 0 (G heads of
-// d), k heads at column G d, v heads at column 2 G d (H heads of dv). a_raw: [rows, H d] decay pre-activations;
-// b_raw: rows of stride ld_b, head h at column b_col + h. state: [slots, H, dv, d]. out: [rows, H dv].
+// An asynchronous copy of 4 or 16 bytes from global to shared memory.
+__device__ __forceinline__ void cp_async_f(float* dst, const float* src, bool wide) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  if (wide) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Where key channel r of a staged vector lies in shared memory: thread s of a value column holds the NR consecutive
+// channels s NR .. s NR + NR - 1 and reads them 16 bytes at a time; four floats of padding after every NR keep the
+// NS threads of a column on different banks.
+template <int NR> __device__ __forceinline__ int staged_at(int r) { return (r / NR) * (NR + 4) + r % NR; }
+
+// Per row, in place: q and k heads (G heads of d at columns 0 and G d of qkv) become unit vectors, q times d^(-1/2);
+// the decay pre-activations a_raw [rows, H d] become g = exp(-exp(A_log[h]) softplus(a + dt_bias)); the gate
+// pre-activation of head h (column b_col + h of b_raw) becomes sigmoid. One block per row.
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(float* __restrict__ qkv, int ld, float* __restrict__ a_raw, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, float* __restrict__ b_raw, int ld_b, int b_col,
+                     const int* __restrict__ seq_of_row, int H, int G, int d) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  if (seq_of_row[row] < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float qscale = rsqrtf((float)d);
+  for (int v = warp; v < 2 * G; v += 8) {  // q heads, then k heads
+    float* x = qkv + row * ld + (size_t)v * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
+    const float inv = (v < G ? qscale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
+    for (int i = lane; i < d; i += 32) x[i] *= inv;
+  }
+  float* ar = a_raw + row * H * d;
+  for (int i = threadIdx.x; i < H * d; i += 256)
+    ar[i] = expf(-expf(a_log[i / d]) * softplusf_(ar[i] + dt_bias[i]));
+  if (threadIdx.x < H) {
+    float* b = b_raw + row * ld_b + b_col + threadIdx.x;
+    *b = sigmoidf_(*b);
+  }
+}
+
+// qkv: 32-bit rows of stride ld, prepared: unit q heads at column 0 (G heads of d), unit k heads at column G d, v
+// heads at column 2 G d (H heads of dv). g: [rows, H d] decays; beta: rows of stride ld_b, head h at column
+// b_col + h. state: [slots, H, dv, d]. out: [rows, H dv]. Two buffers of TC tokens: the next tokens' vectors are
+// copied (cp.async) while these are worked through.
 template <int NR>
-__global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ a_raw,
-                                  const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-                                  const float* __restrict__ b_raw, int ld_b, int b_col, float* __restrict__ state,
+__global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ g,
+                                  const float* __restrict__ beta, int ld_b, int b_col, float* __restrict__ state,
                                   float* __restrict__ out, const int* __restrict__ req_row0,
                                   const int* __restrict__ req_count, const int* __restrict__ slots, int H, int G,
-                                  int d, int dv, int NS, int PB, int TC) {
+                                  int d, int dv, int NS, int PB, int TC, int wide) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
@@ -43,102 +88,130 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
   const int slot = slots[rq], n = req_count[rq], r0 = req_row0[rq];
   if (slot < 0 || n <= 0) return;
   const int kvh = h / (H / G);
-  const int dp = NS * NR;  // key channels padded to what the threads hold
-  float* sq = sm;                      // [TC][dp]
-  float* sk = sq + (size_t)TC * dp;    // [TC][dp]
-  float* sg = sk + (size_t)TC * dp;    // [TC][dp]
-  float* sv = sg + (size_t)TC * dp;    // [TC][PB]
-  float* sb = sv + (size_t)TC * PB;    // [TC]
+  const int dpp = NS * (NR + 4);               // a staged vector with its padding
+  const int per = (3 * dpp + PB + 1 + 3) & ~3;  // a token: q, k, g, the block's values, beta
   const int col_local = threadIdx.x / NS, s = threadIdx.x % NS;
   const int col = blockIdx.z * PB + col_local;
   const bool live = col_local < PB && col < dv;
   float S[NR];
   float* st = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
 #pragma unroll
-  for (int i = 0; i < NR; ++i) S[i] = (live && s + i * NS < d) ? st[s + i * NS] : 0.f;
-  const float A = expf(a_log[h]);
-  const float qscale = rsqrtf((float)d);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-  for (int t0 = 0; t0 < n; t0 += TC) {
+  for (int i = 0; i < NR; ++i) S[i] = (live && s * NR + i < d) ? st[s * NR + i] : 0.f;
+  // what no copy writes: channels beyond d (q = k = 0, g = 1) and the padding
+  for (int e = threadIdx.x; e < 2 * TC * per; e += blockDim.x) {
+    const int w = e % per;
+    sm[e] = (w >= 2 * dpp && w < 3 * dpp) ? 1.f : 0.f;
+  }
+  __syncthreads();
+  auto stage = [&](int t0, int buf) {
     const int nt = n - t0 < TC ? n - t0 : TC;
-    __syncthreads();  // the previous chunk has been read
-    for (int t = warp; t < nt; t += n_warps) {
-      const float* row = qkv + (size_t)(r0 + t0 + t) * ld;
-      const float* qr = row + (size_t)kvh * d;
-      const float* kr = row + (size_t)(G + kvh) * d;
-      float qq = 0.f, kk = 0.f;
-      for (int i = lane; i < d; i += 32) { qq = fmaf(qr[i], qr[i], qq); kk = fmaf(kr[i], kr[i], kk); }
-      const float iq = qscale / sqrtf(warp_sum(qq) + 1e-6f), ik = 1.f / sqrtf(warp_sum(kk) + 1e-6f);
-      const float* ar = a_raw + (size_t)(r0 + t0 + t) * H * d + (size_t)h * d;
-      for (int i = lane; i < dp; i += 32) {
-        const bool in = i < d;
-        sq[(size_t)t * dp + i] = in ? qr[i] * iq : 0.f;
-        sk[(size_t)t * dp + i] = in ? kr[i] * ik : 0.f;
-        sg[(size_t)t * dp + i] = in ? expf(-A * softplusf_(ar[i] + dt_bias[(size_t)h * d + i])) : 1.f;
-      }
-      const float* vr = row + (size_t)2 * G * d + (size_t)h * dv + (size_t)blockIdx.z * PB;
-      for (int i = lane; i < PB; i += 32) sv[(size_t)t * PB + i] = blockIdx.z * PB + i < dv ? vr[i] : 0.f;
-      if (lane == 0) sb[t] = sigmoidf_(b_raw[(size_t)(r0 + t0 + t) * ld_b + b_col + h]);
+    float* base = sm + (size_t)buf * TC * per;
+    const int step = wide ? 4 : 1, units = d / step;
+    for (int e = threadIdx.x; e < nt * 3 * units; e += blockDim.x) {
+      const int t = e / (3 * units), u = e % (3 * units), which = u / units, r = (u % units) * step;
+      const size_t row = (size_t)(r0 + t0 + t);
+      const float* src = which == 0 ? qkv + row * ld + (size_t)kvh * d + r
+                       : which == 1 ? qkv + row * ld + (size_t)(G + kvh) * d + r
+                                    : g + row * H * d + (size_t)h * d + r;
+      cp_async_f(base + (size_t)t * per + which * dpp + staged_at<NR>(r), src, wide);
     }
+    for (int e = threadIdx.x; e < nt * (PB + 1); e += blockDim.x) {
+      const int t = e / (PB + 1), i = e % (PB + 1);
+      const size_t row = (size_t)(r0 + t0 + t);
+      if (i == PB) cp_async_f(base + (size_t)t * per + 3 * dpp + PB, beta + row * ld_b + b_col + h, false);
+      else if (blockIdx.z * PB + i < dv)
+        cp_async_f(base + (size_t)t * per + 3 * dpp + i, qkv + row * ld + (size_t)2 * G * d + (size_t)h * dv + blockIdx.z * PB + i, false);
+    }
+    cp_async_commit();
+  };
+  const int cv = col_local < PB ? col_local : PB - 1;
+  const int n_chunks = (n + TC - 1) / TC;
+  stage(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) { stage((c + 1) * TC, (c + 1) & 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
     __syncthreads();
-    {  // every thread of a warp takes part (the sums shuffle across whole warps); spare threads work on zeros
-      const int cv = col_local < PB ? col_local : PB - 1;
-      for (int t = 0; t < nt; ++t) {
-        const float* gq = sq + (size_t)t * dp + s;
-        const float* gk = sk + (size_t)t * dp + s;
-        const float* gg = sg + (size_t)t * dp + s;
-        float part = 0.f;
+    const int t0 = c * TC, nt = n - t0 < TC ? n - t0 : TC;
+    const float* base = sm + (size_t)(c & 1) * TC * per;
+    // every thread of a warp takes part (the sums shuffle across whole warps); spare threads work on zeros
+    for (int t = 0; t < nt; ++t) {
+      const float* tok = base + (size_t)t * per;
+      const float4* gq = reinterpret_cast<const float4*>(tok + s * (NR + 4));
+      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + s * (NR + 4));
+      const float4* gg = reinterpret_cast<const float4*>(tok + 2 * dpp + s * (NR + 4));
+      float kk[NR];
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < NR; ++i) {
-          S[i] *= gg[i * NS];
-          part = fmaf(S[i], gk[i * NS], part);
-        }
-        part = group_sum(part, NS);
-        const float u = sb[t] * (sv[(size_t)t * PB + cv] - part);
-        float po = 0.f;
-#pragma unroll
-        for (int i = 0; i < NR; ++i) {
-          S[i] = fmaf(gk[i * NS], u, S[i]);
-          po = fmaf(S[i], gq[i * NS], po);
-        }
-        po = group_sum(po, NS);
-        if (s == 0 && live) out[(size_t)(r0 + t0 + t) * H * dv + (size_t)h * dv + col] = po;
+      for (int i = 0; i < NR / 4; ++i) {
+        const float4 gv = gg[i], kv4 = gk[i];
+        kk[4 * i] = kv4.x; kk[4 * i + 1] = kv4.y; kk[4 * i + 2] = kv4.z; kk[4 * i + 3] = kv4.w;
+        S[4 * i] *= gv.x; S[4 * i + 1] *= gv.y; S[4 * i + 2] *= gv.z; S[4 * i + 3] *= gv.w;
+        p0 = fmaf(S[4 * i], kv4.x, p0); p1 = fmaf(S[4 * i + 1], kv4.y, p1);
+        p2 = fmaf(S[4 * i + 2], kv4.z, p2); p3 = fmaf(S[4 * i + 3], kv4.w, p3);
       }
+      const float part = group_sum((p0 + p1) + (p2 + p3), NS);
+      const float u = tok[3 * dpp + PB] * (tok[3 * dpp + cv] - part);
+      p0 = p1 = p2 = p3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR / 4; ++i) {
+        const float4 qv = gq[i];
+        S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]); S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]); S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
+        p0 = fmaf(S[4 * i], qv.x, p0); p1 = fmaf(S[4 * i + 1], qv.y, p1);
+        p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
+      }
+      const float po = group_sum((p0 + p1) + (p2 + p3), NS);
+      if (s == 0 && live) out[(size_t)(r0 + t0 + t) * H * dv + (size_t)h * dv + col] = po;
     }
+    __syncthreads();  // the buffer is free for the copies of the chunk after next
   }
   if (live) {
 #pragma unroll
     for (int i = 0; i < NR; ++i)
-      if (s + i * NS < d) st[s + i * NS] = S[i];
+      if (s * NR + i < d) st[s * NR + i] = S[i];
   }
 }
 
-// proj: 32-bit rows of stride ld: q heads at q_col (H heads of d), k at k_col, v at v_col (H heads of dv), the raw
-// input gate of head h at i_col + h, the raw forget gate at f_col + h (their biases i_bias, f_bias are added here).
+// Per row, in place: the raw input gate of head h (column i_col + h of proj) becomes cap tanh((x + b_i) / cap), the
+// raw forget gate (column f_col + h) becomes logsigmoid(cap tanh((x + b_f) / cap)).
+__global__ void mlstm_prepare_kernel(float* __restrict__ proj, int ld, int i_col, int f_col,
+                                     const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
+                                     int n_rows, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_rows * H) return;
+  float* row = proj + (size_t)(e / H) * ld;
+  const int h = e % H;
+  row[i_col + h] = cap * tanhf((row[i_col + h] + (i_bias ? i_bias[h] : 0.f)) / cap);
+  row[f_col + h] = log_sigmoidf_(cap * tanhf((row[f_col + h] + (f_bias ? f_bias[h] : 0.f)) / cap));
+}
+
+// proj: 32-bit rows of stride ld, prepared: q heads at q_col (H heads of d), k at k_col, v at v_col (H heads of dv),
+// the log input gate of head h at i_col + h, the log forget gate at f_col + h.
 // mem: [slots, H, dv, d]; nrm: [slots, H, d]; mx: [slots, H]. out: [rows, H dv].
 // The block's columns are its PB value columns and one more that carries n (its "value" is 1), so n . q comes out
-// of the same loop; the division waits until the chunk's sums are in shared memory.
+// of the same loop; the division waits until the chunk's sums are in shared memory. q enters unscaled: the sums
+// are linear in it, so d^(-1/2) multiplies them afterwards.
 template <int NR>
 __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int i_col,
-                                  int f_col, const float* __restrict__ i_bias, const float* __restrict__ f_bias,
-                                  float cap, float* __restrict__ mem, float* __restrict__ nrm, float* __restrict__ mx,
+                                  int f_col, float* __restrict__ mem, float* __restrict__ nrm, float* __restrict__ mx,
                                   float* __restrict__ out, const int* __restrict__ req_row0,
                                   const int* __restrict__ req_count, const int* __restrict__ slots, int H, int d,
-                                  int dv, int NS, int PB, int TC) {
+                                  int dv, int NS, int PB, int TC, int wide) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.x, rq = blockIdx.y;
   const int slot = slots[rq], n = req_count[rq], r0 = req_row0[rq];
   if (slot < 0 || n <= 0) return;
-  const int dp = NS * NR;
-  float* sq = sm;                          // [TC][dp]
-  float* sk = sq + (size_t)TC * dp;        // [TC][dp]
-  float* sv = sk + (size_t)TC * dp;        // [TC][PB + 1]
-  float* so = sv + (size_t)TC * (PB + 1);  // [TC][PB + 1]
+  const int dpp = NS * (NR + 4);
+  const int per = (2 * dpp + (PB + 1) + 2 + 3) & ~3;  // a token: q, k, the block's values and a 1, the two gates
+  float* so = sm + (size_t)2 * TC * per;     // [TC][PB + 1] the chunk's sums
   float* keep = so + (size_t)TC * (PB + 1);  // [TC] e^(f + m - m')
-  float* take = keep + TC;                 // [TC] e^(i - m')
-  float* floor_ = take + TC;               // [TC] e^(-m')
+  float* take = keep + TC;                   // [TC] e^(i - m')
+  float* floor_ = take + TC;                 // [TC] e^(-m')
+  float* ms = floor_ + TC;                   // [TC + 1] m before each token of the chunk, and after the last
   const int col_local = threadIdx.x / NS, s = threadIdx.x % NS;
   const bool is_n = col_local == PB;
   const int col = blockIdx.z * PB + col_local;
@@ -147,52 +220,72 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
   float* st = is_n ? nrm + ((size_t)slot * H + h) * d
                    : mem + (((size_t)slot * H + h) * dv + (col < dv ? col : 0)) * d;
 #pragma unroll
-  for (int i = 0; i < NR; ++i) S[i] = (live && col_local <= PB && s + i * NS < d) ? st[s + i * NS] : 0.f;
-  float m = mx[(size_t)slot * H + h];  // thread 0 carries it
+  for (int i = 0; i < NR; ++i) S[i] = (live && s * NR + i < d) ? st[s * NR + i] : 0.f;
+  for (int e = threadIdx.x; e < 2 * TC * per; e += blockDim.x) sm[e] = (e % per == 2 * dpp + PB) ? 1.f : 0.f;
+  if (threadIdx.x == 0) ms[0] = mx[(size_t)slot * H + h];
+  __syncthreads();
   const float qscale = rsqrtf((float)d);
-  const float bi = i_bias ? i_bias[h] : 0.f, bf = f_bias ? f_bias[h] : 0.f;
-  for (int t0 = 0; t0 < n; t0 += TC) {
+  auto stage = [&](int t0, int buf) {
     const int nt = n - t0 < TC ? n - t0 : TC;
+    float* base = sm + (size_t)buf * TC * per;
+    const int step = wide ? 4 : 1, units = d / step;
+    for (int e = threadIdx.x; e < nt * 2 * units; e += blockDim.x) {
+      const int t = e / (2 * units), u = e % (2 * units), which = u / units, r = (u % units) * step;
+      const float* src = proj + (size_t)(r0 + t0 + t) * ld + (which ? k_col : q_col) + (size_t)h * d + r;
+      cp_async_f(base + (size_t)t * per + which * dpp + staged_at<NR>(r), src, wide);
+    }
+    for (int e = threadIdx.x; e < nt * (PB + 2); e += blockDim.x) {
+      const int t = e / (PB + 2), i = e % (PB + 2);
+      const float* row = proj + (size_t)(r0 + t0 + t) * ld;
+      float* tok = base + (size_t)t * per + 2 * dpp;
+      if (i == PB) cp_async_f(tok + PB + 1, row + i_col + h, false);
+      else if (i == PB + 1) cp_async_f(tok + PB + 2, row + f_col + h, false);
+      else if (blockIdx.z * PB + i < dv) cp_async_f(tok + i, row + v_col + (size_t)h * dv + blockIdx.z * PB + i, false);
+    }
+    cp_async_commit();
+  };
+  const int cv = col_local <= PB ? col_local : PB;
+  const int n_chunks = (n + TC - 1) / TC;
+  stage(0, 0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) { stage((c + 1) * TC, (c + 1) & 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * dp; e += blockDim.x) {
-      const int t = e / dp, i = e % dp;
-      const float* row = proj + (size_t)(r0 + t0 + t) * ld;
-      sq[e] = i < d ? row[q_col + (size_t)h * d + i] * qscale : 0.f;
-      sk[e] = i < d ? row[k_col + (size_t)h * d + i] : 0.f;
-    }
-    for (int e = threadIdx.x; e < nt * (PB + 1); e += blockDim.x) {
-      const int t = e / (PB + 1), i = e % (PB + 1);
-      const float* row = proj + (size_t)(r0 + t0 + t) * ld;
-      sv[e] = i == PB ? 1.f : (blockIdx.z * PB + i < dv ? row[v_col + (size_t)h * dv + blockIdx.z * PB + i] : 0.f);
-    }
-    if (threadIdx.x == 0) {
+    const int t0 = c * TC, nt = n - t0 < TC ? n - t0 : TC;
+    const float* base = sm + (size_t)(c & 1) * TC * per;
+    if (threadIdx.x == 0) {  // the running maximum is a chain of one add and one max per token
+      float m = ms[0];
       for (int t = 0; t < nt; ++t) {
-        const float* row = proj + (size_t)(r0 + t0 + t) * ld;
-        const float gi = cap * tanhf((row[i_col + h] + bi) / cap);
-        const float gf = log_sigmoidf_(cap * tanhf((row[f_col + h] + bf) / cap));
-        const float m_new = fmaxf(gf + m, gi);
-        keep[t] = expf(gf + m - m_new);
-        take[t] = expf(gi - m_new);
-        floor_[t] = expf(-m_new);
-        m = m_new;
+        const float* tok = base + (size_t)t * per + 2 * dpp;
+        m = fmaxf(tok[PB + 2] + m, tok[PB + 1]);
+        ms[t + 1] = m;
       }
     }
     __syncthreads();
-    {  // every thread of a warp takes part (the sums shuffle across whole warps); spare threads work on zeros
-      const int cv = col_local <= PB ? col_local : PB;
-      for (int t = 0; t < nt; ++t) {
-        const float* gq = sq + (size_t)t * dp + s;
-        const float* gk = sk + (size_t)t * dp + s;
-        const float kp = keep[t], w = take[t] * sv[(size_t)t * (PB + 1) + cv];
-        float po = 0.f;
+    if (threadIdx.x < nt) {
+      const int t = threadIdx.x;
+      const float* tok = base + (size_t)t * per + 2 * dpp;
+      keep[t] = expf(tok[PB + 2] + ms[t] - ms[t + 1]);
+      take[t] = expf(tok[PB + 1] - ms[t + 1]);
+      floor_[t] = expf(-ms[t + 1]);
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float* tok = base + (size_t)t * per;
+      const float4* gq = reinterpret_cast<const float4*>(tok + s * (NR + 4));
+      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + s * (NR + 4));
+      const float kp = keep[t], w = take[t] * tok[2 * dpp + cv];
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < NR; ++i) {
-          S[i] = fmaf(kp, S[i], w * gk[i * NS]);
-          po = fmaf(S[i], gq[i * NS], po);
-        }
-        po = group_sum(po, NS);
-        if (s == 0 && col_local <= PB) so[(size_t)t * (PB + 1) + col_local] = po;
+      for (int i = 0; i < NR / 4; ++i) {
+        const float4 kv4 = gk[i], qv = gq[i];
+        S[4 * i] = fmaf(kp, S[4 * i], w * kv4.x); S[4 * i + 1] = fmaf(kp, S[4 * i + 1], w * kv4.y);
+        S[4 * i + 2] = fmaf(kp, S[4 * i + 2], w * kv4.z); S[4 * i + 3] = fmaf(kp, S[4 * i + 3], w * kv4.w);
+        p0 = fmaf(S[4 * i], qv.x, p0); p1 = fmaf(S[4 * i + 1], qv.y, p1);
+        p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
       }
+      const float po = group_sum((p0 + p1) + (p2 + p3), NS) * qscale;
+      if (s == 0 && col_local <= PB) so[(size_t)t * (PB + 1) + col_local] = po;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < nt * PB; e += blockDim.x) {
@@ -202,13 +295,15 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
         out[(size_t)(r0 + t0 + t) * H * dv + (size_t)h * dv + blockIdx.z * PB + i] = so[(size_t)t * (PB + 1) + i] / den;
       }
     }
+    if (threadIdx.x == 0) ms[0] = ms[nt];
+    __syncthreads();  // the buffers and the chunk's sums are free again
   }
   if (live && col_local <= PB && (!is_n || blockIdx.z == 0)) {
 #pragma unroll
     for (int i = 0; i < NR; ++i)
-      if (s + i * NS < d) st[s + i * NS] = S[i];
+      if (s * NR + i < d) st[s * NR + i] = S[i];
   }
-  if (threadIdx.x == 0 && blockIdx.z == 0) mx[(size_t)slot * H + h] = m;
+  if (threadIdx.x == 0 && blockIdx.z == 0) mx[(size_t)slot * H + h] = ms[0];
 }
 
 // o: [rows, H dv] 32-bit. out[r, h, j] = o / sqrt(mean_j o^2 + eps) * w[h * w_head + j] * sigmoid(gate[r, h dv + j]);
@@ -253,29 +348,36 @@ int round_nr(int nr) { return nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32; }
 
 CUCA_API int cuca_matrix_state_max_dim() { return 32 * MAXR; }
 
-CUCA_API int cuca_delta_scan(const float* qkv, int ld, const float* a_raw, const float* dt_bias, const float* a_log,
-                             const float* b_raw, int ld_b, int b_col, float* state, float* out, const int* req_row0,
-                             const int* req_count, const int* slots, int n_seqs, int H, int G, int d, int dv,
-                             cudaStream_t stream) {
-  if (n_seqs == 0) return 0;
+// qkv, a_raw and the gate column of b_raw are rewritten in place by the preparing kernel (see there), then scanned.
+CUCA_API int cuca_delta_scan(float* qkv, int ld, float* a_raw, const float* dt_bias, const float* a_log,
+                             float* b_raw, int ld_b, int b_col, float* state, float* out, const int* seq_of_row,
+                             const int* req_row0, const int* req_count, const int* slots, int n_rows, int n_seqs, int H,
+                             int G, int d, int dv, cudaStream_t stream) {
+  if (n_seqs == 0 || n_rows == 0) return 0;
   CUCA_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "delta_scan: bad sizes heads=%d key heads=%d dim=%d vdim=%d",
                H, G, d, dv);
-  CUCA_REQUIRE(n_seqs <= 65535, "delta_scan: %d requests exceed the launch limit", n_seqs);
+  CUCA_REQUIRE(n_seqs <= 65535 && H <= 256, "delta_scan: %d requests or %d heads exceed the launch limits", n_seqs, H);
   int ns, nr;
   CUCA_REQUIRE(split_rows(d, &ns, &nr), "delta_scan: %d key channels exceed %d", d, 32 * MAXR);
   nr = round_nr(nr);
+  cuca_launch(delta_prepare_kernel, dim3(n_rows), dim3(256), 0, stream, true, qkv, ld, a_raw, dt_bias, a_log, b_raw, ld_b,
+              b_col, seq_of_row, H, G, d);
+  CUCA_CHECK_LAUNCH("delta_prepare");
   int pb = 128 / ns;
   pb = pb > dv ? dv : pb;
   const int threads = (pb * ns + 31) / 32 * 32;
-  const int dp = ns * nr;
-  int tc = 40960 / ((3 * dp + pb + 1) * 4);
+  const int per = (3 * ns * (nr + 4) + pb + 1 + 3) & ~3;
+  int tc = 46000 / (2 * per * 4);
   tc = tc > 16 ? 16 : tc;
   CUCA_REQUIRE(tc >= 1, "delta_scan: a token of %d key channels does not fit shared memory", d);
-  const size_t smem = (size_t)tc * (3 * dp + pb + 1) * 4;
+  const size_t smem = (size_t)2 * tc * per * 4;
+  // 16-byte copies where every source is aligned for them
+  const int wide = d % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)a_raw & 15) == 0;
   dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
 #define DS(NR)                                                                                                    \
-  cuca_launch(delta_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, qkv, ld, a_raw, dt_bias, a_log, b_raw, \
-              ld_b, b_col, state, out, req_row0, req_count, slots, H, G, d, dv, ns, pb, tc)
+  cuca_launch(delta_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)qkv, ld,              \
+              (const float*)a_raw, (const float*)b_raw, ld_b, b_col, state, out, req_row0, req_count, slots, H, G, d, \
+              dv, ns, pb, tc, wide)
   if (nr == 4) DS(4);
   else if (nr == 8) DS(8);
   else if (nr == 16) DS(16);
@@ -285,30 +387,34 @@ CUCA_API int cuca_delta_scan(const float* qkv, int ld, const float* a_raw, const
   return 0;
 }
 
-CUCA_API int cuca_mlstm_scan(const float* proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
+// The two gate columns of proj are rewritten in place by the preparing kernel (see there), then scanned.
+CUCA_API int cuca_mlstm_scan(float* proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                              const float* i_bias, const float* f_bias, float cap, float* mem, float* nrm, float* mx,
-                             float* out, const int* req_row0, const int* req_count, const int* slots, int n_seqs,
-                             int H, int d, int dv, cudaStream_t stream) {
-  if (n_seqs == 0) return 0;
+                             float* out, const int* req_row0, const int* req_count, const int* slots, int n_rows,
+                             int n_seqs, int H, int d, int dv, cudaStream_t stream) {
+  if (n_seqs == 0 || n_rows == 0) return 0;
   CUCA_REQUIRE(H > 0 && d > 0 && dv > 0 && cap > 0.f, "mlstm_scan: bad sizes heads=%d dim=%d vdim=%d cap=%g", H, d, dv,
                (double)cap);
   CUCA_REQUIRE(n_seqs <= 65535, "mlstm_scan: %d requests exceed the launch limit", n_seqs);
   int ns, nr;
   CUCA_REQUIRE(split_rows(d, &ns, &nr), "mlstm_scan: %d key channels exceed %d", d, 32 * MAXR);
   nr = round_nr(nr);
+  cuca_launch(mlstm_prepare_kernel, dim3((n_rows * H + 127) / 128), dim3(128), 0, stream, true, proj, ld, i_col, f_col,
+              i_bias, f_bias, cap, n_rows, H);
+  CUCA_CHECK_LAUNCH("mlstm_prepare");
   int pb = 128 / ns - 1;  // one more column carries n
   pb = pb < 1 ? 1 : (pb > dv ? dv : pb);
   const int threads = ((pb + 1) * ns + 31) / 32 * 32;
-  const int dp = ns * nr;
-  const int per = 2 * dp + 2 * (pb + 1) + 3;
-  int tc = 40960 / (per * 4);
+  const int per = (2 * ns * (nr + 4) + (pb + 1) + 2 + 3) & ~3;
+  int tc = 46000 / ((2 * per + pb + 6) * 4);
   tc = tc > 16 ? 16 : tc;
   CUCA_REQUIRE(tc >= 1, "mlstm_scan: a token of %d key channels does not fit shared memory", d);
-  const size_t smem = (size_t)tc * per * 4;
+  const size_t smem = ((size_t)2 * tc * per + (size_t)tc * (pb + 1) + 4 * tc + 1) * 4;
+  const int wide = d % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && ((uintptr_t)proj & 15) == 0;
   dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
 #define MS(NR)                                                                                                      \
-  cuca_launch(mlstm_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, proj, ld, q_col, k_col, v_col, i_col,   \
-              f_col, i_bias, f_bias, cap, mem, nrm, mx, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc)
+  cuca_launch(mlstm_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, k_col,   \
+              v_col, i_col, f_col, mem, nrm, mx, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide)
   if (nr == 4) MS(4);
   else if (nr == 8) MS(8);
   else if (nr == 16) MS(16);

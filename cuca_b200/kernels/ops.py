@@ -871,12 +871,15 @@ MATRIX_STATE_MAX_DIM = 1024  # `cuca_matrix_state_max_dim` says the same
 
 
 def delta_scan(qkv, a_raw, dt_bias, a_log, b_src, b_col, state, out, step, H, G, d, dv) -> None:
-    """The delta rule with a decay per key channel along every request's rows (see `parts/recurrent.py:GatedDelta`)."""
+    """The delta rule with a decay per key channel along every request's rows (see `parts/recurrent.py:GatedDelta`).
+    `qkv`, `a_raw` and column `b_col`.. of `b_src` hold pre-activations and are rewritten in place (unit vectors,
+    decays, the write gate) before the scan; two launches."""
     _cuda(qkv, a_raw, dt_bias, a_log, b_src, state, out)
     library.check(library.load().cuca_delta_scan(
         _p(qkv), qkv.stride(0), _p(a_raw), _p(dt_bias), _p(a_log), _p(b_src), b_src.stride(0), int(b_col), _p(state),
-        _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots), step.n_seqs, H, G, d, dv, _stream()),
-        "delta_scan")
+        _p(out), _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots), qkv.shape[0], step.n_seqs,
+        H, G, d, dv, _stream()), "delta_scan")
+    library.launches += 1
 
 
 def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem, nrm, mx, out, step, H, d, dv) -> None:
@@ -884,7 +887,8 @@ def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem
     library.check(library.load().cuca_mlstm_scan(
         _p(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(i_col), int(f_col), _p(i_bias), _p(f_bias),
         float(cap), _p(mem), _p(nrm), _p(mx), _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots),
-        step.n_seqs, H, d, dv, _stream()), "mlstm_scan")
+        proj.shape[0], step.n_seqs, H, d, dv, _stream()), "mlstm_scan")
+    library.launches += 1  # the gates are prepared by a launch of their own
 
 
 def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:
