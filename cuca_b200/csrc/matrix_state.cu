@@ -10,9 +10,11 @@
 // the step in order from the state its slot holds, leaving the new state there. A value column's state rows live in
 // the registers of NS neighbouring threads (thread s holds NR consecutive rows); a token's vectors are copied to
 // shared memory a few tokens ahead of their use. The arithmetic of a token does not depend on where the sequence was
-// cut into steps or chunks.
+// cut into steps or chunks; how many threads share a column's sums (and so the order of those sums) depends on how
+// many columns the launch has.
 #include "common.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -24,7 +26,11 @@ __device__ __forceinline__ float log_sigmoidf_(float v) { return v < 0.f ? v - l
 
 // sum over the NS neighbouring threads of a value column (NS a power of two, at most 32)
 __device__ __forceinline__ float group_sum(float v, int NS) {
-  for (int o = NS >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (NS >= 32) v += __shfl_xor_sync(0xffffffffu, v, 16);
+  if (NS >= 16) v += __shfl_xor_sync(0xffffffffu, v, 8);
+  if (NS >= 8) v += __shfl_xor_sync(0xffffffffu, v, 4);
+  if (NS >= 4) v += __shfl_xor_sync(0xffffffffu, v, 2);
+  if (NS >= 2) v += __shfl_xor_sync(0xffffffffu, v, 1);
   return v;
 }
 
@@ -40,13 +46,15 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Where key channel r of a staged vector lies in shared memory: thread s of a value column holds the NR consecutive
 // channels s NR .. s NR + NR - 1 and reads them 16 bytes at a time; four floats of padding after every NR keep the
 // NS threads of a column on different banks.
-template <int NR> __device__ __forceinline__ int staged_at(int r) { return (r / NR) * (NR + 4) + r % NR; }
+// (Four channels a thread are 16 bytes a thread: contiguous, nothing to pad.)
+template <int NR> __device__ __forceinline__ constexpr int staged_stride() { return NR == 4 ? 4 : NR + 4; }
+template <int NR> __device__ __forceinline__ int staged_at(int r) { return (r / NR) * staged_stride<NR>() + r % NR; }
 
 // Per row, in place: q and k heads (G heads of d at columns 0 and G d of qkv) become unit vectors, q times d^(-1/2);
-// the decay pre-activations a_raw [rows, H d] become g = exp(-exp(A_log[h]) softplus(a + dt_bias)); the gate
+// the decay pre-activations a_raw (rows of stride ld_a, H d values) become g = exp(-exp(A_log[h]) softplus(a + dt_bias)); the gate
 // pre-activation of head h (column b_col + h of b_raw) becomes sigmoid. One block per row.
 __global__ void __launch_bounds__(256)
-delta_prepare_kernel(float* __restrict__ qkv, int ld, float* __restrict__ a_raw, const float* __restrict__ dt_bias,
+delta_prepare_kernel(float* __restrict__ qkv, int ld, float* __restrict__ a_raw, int ld_a, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, float* __restrict__ b_raw, int ld_b, int b_col,
                      const int* __restrict__ seq_of_row, int H, int G, int d) {
   pdl_trigger();
@@ -62,7 +70,7 @@ delta_prepare_kernel(float* __restrict__ qkv, int ld, float* __restrict__ a_raw,
     const float inv = (v < G ? qscale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
     for (int i = lane; i < d; i += 32) x[i] *= inv;
   }
-  float* ar = a_raw + row * H * d;
+  float* ar = a_raw + row * ld_a;
   for (int i = threadIdx.x; i < H * d; i += 256)
     ar[i] = expf(-expf(a_log[i / d]) * softplusf_(ar[i] + dt_bias[i]));
   if (threadIdx.x < H) {
@@ -72,11 +80,11 @@ delta_prepare_kernel(float* __restrict__ qkv, int ld, float* __restrict__ a_raw,
 }
 
 // qkv: 32-bit rows of stride ld, prepared: unit q heads at column 0 (G heads of d), unit k heads at column G d, v
-// heads at column 2 G d (H heads of dv). g: [rows, H d] decays; beta: rows of stride ld_b, head h at column
+// heads at column 2 G d (H heads of dv). g: rows of stride ld_g, H d decays; beta: rows of stride ld_b, head h at column
 // b_col + h. state: [slots, H, dv, d]. out: [rows, H dv]. Two buffers of TC tokens: the next tokens' vectors are
 // copied (cp.async) while these are worked through.
 template <int NR>
-__global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ g,
+__global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ g, int ld_g,
                                   const float* __restrict__ beta, int ld_b, int b_col, float* __restrict__ state,
                                   float* __restrict__ out, const int* __restrict__ req_row0,
                                   const int* __restrict__ req_count, const int* __restrict__ slots, int H, int G,
@@ -88,7 +96,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
   const int slot = slots[rq], n = req_count[rq], r0 = req_row0[rq];
   if (slot < 0 || n <= 0) return;
   const int kvh = h / (H / G);
-  const int dpp = NS * (NR + 4);               // a staged vector with its padding
+  const int dpp = NS * staged_stride<NR>();     // a staged vector with its padding
   const int per = (3 * dpp + PB + 1 + 3) & ~3;  // a token: q, k, g, the block's values, beta
   const int col_local = threadIdx.x / NS, s = threadIdx.x % NS;
   const int col = blockIdx.z * PB + col_local;
@@ -97,10 +105,15 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
   float* st = state + (((size_t)slot * H + h) * dv + (live ? col : 0)) * d;
 #pragma unroll
   for (int i = 0; i < NR; ++i) S[i] = (live && s * NR + i < d) ? st[s * NR + i] : 0.f;
-  // what no copy writes: channels beyond d (q = k = 0, g = 1) and the padding
-  for (int e = threadIdx.x; e < 2 * TC * per; e += blockDim.x) {
-    const int w = e % per;
-    sm[e] = (w >= 2 * dpp && w < 3 * dpp) ? 1.f : 0.f;
+  // what no copy writes: channels from d on (q = k = 0, g = 1) and the values of columns from dv on
+  {
+    const int spare = NS * NR - d, fill = 3 * spare + PB;
+    for (int e = threadIdx.x; e < 2 * TC * fill; e += blockDim.x) {
+      const int t = e / fill, w = e % fill;
+      float* tok = sm + (size_t)t * per;
+      if (w < 3 * spare) tok[(w / spare) * dpp + staged_at<NR>(d + w % spare)] = w / spare == 2 ? 1.f : 0.f;
+      else tok[3 * dpp + (w - 3 * spare)] = 0.f;
+    }
   }
   __syncthreads();
   auto stage = [&](int t0, int buf) {
@@ -112,7 +125,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
       const size_t row = (size_t)(r0 + t0 + t);
       const float* src = which == 0 ? qkv + row * ld + (size_t)kvh * d + r
                        : which == 1 ? qkv + row * ld + (size_t)(G + kvh) * d + r
-                                    : g + row * H * d + (size_t)h * d + r;
+                                    : g + row * ld_g + (size_t)h * d + r;
       cp_async_f(base + (size_t)t * per + which * dpp + staged_at<NR>(r), src, wide);
     }
     for (int e = threadIdx.x; e < nt * (PB + 1); e += blockDim.x) {
@@ -134,11 +147,14 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
     const int t0 = c * TC, nt = n - t0 < TC ? n - t0 : TC;
     const float* base = sm + (size_t)(c & 1) * TC * per;
     // every thread of a warp takes part (the sums shuffle across whole warps); spare threads work on zeros
-    for (int t = 0; t < nt; ++t) {
-      const float* tok = base + (size_t)t * per;
-      const float4* gq = reinterpret_cast<const float4*>(tok + s * (NR + 4));
-      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + s * (NR + 4));
-      const float4* gg = reinterpret_cast<const float4*>(tok + 2 * dpp + s * (NR + 4));
+    const float* tok = base;
+    float* po_at = out + (size_t)(r0 + t0) * H * dv + (size_t)h * dv + col;
+    const int mine = s * staged_stride<NR>(), extra = 3 * dpp;
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t, tok += per, po_at += H * dv) {
+      const float4* gq = reinterpret_cast<const float4*>(tok + mine);
+      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + mine);
+      const float4* gg = reinterpret_cast<const float4*>(tok + 2 * dpp + mine);
       float kk[NR];
       float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
@@ -150,7 +166,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
         p2 = fmaf(S[4 * i + 2], kv4.z, p2); p3 = fmaf(S[4 * i + 3], kv4.w, p3);
       }
       const float part = group_sum((p0 + p1) + (p2 + p3), NS);
-      const float u = tok[3 * dpp + PB] * (tok[3 * dpp + cv] - part);
+      const float u = tok[extra + PB] * (tok[extra + cv] - part);
       p0 = p1 = p2 = p3 = 0.f;
 #pragma unroll
       for (int i = 0; i < NR / 4; ++i) {
@@ -161,7 +177,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int ld, const f
         p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
       }
       const float po = group_sum((p0 + p1) + (p2 + p3), NS);
-      if (s == 0 && live) out[(size_t)(r0 + t0 + t) * H * dv + (size_t)h * dv + col] = po;
+      if (s == 0 && live) *po_at = po;
     }
     __syncthreads();  // the buffer is free for the copies of the chunk after next
   }
@@ -205,7 +221,7 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
   const int h = blockIdx.x, rq = blockIdx.y;
   const int slot = slots[rq], n = req_count[rq], r0 = req_row0[rq];
   if (slot < 0 || n <= 0) return;
-  const int dpp = NS * (NR + 4);
+  const int dpp = NS * staged_stride<NR>();
   const int per = (2 * dpp + (PB + 1) + 2 + 3) & ~3;  // a token: q, k, the block's values and a 1, the two gates
   float* so = sm + (size_t)2 * TC * per;     // [TC][PB + 1] the chunk's sums
   float* keep = so + (size_t)TC * (PB + 1);  // [TC] e^(f + m - m')
@@ -221,7 +237,15 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
                    : mem + (((size_t)slot * H + h) * dv + (col < dv ? col : 0)) * d;
 #pragma unroll
   for (int i = 0; i < NR; ++i) S[i] = (live && s * NR + i < d) ? st[s * NR + i] : 0.f;
-  for (int e = threadIdx.x; e < 2 * TC * per; e += blockDim.x) sm[e] = (e % per == 2 * dpp + PB) ? 1.f : 0.f;
+  {
+    const int spare = NS * NR - d, fill = 2 * spare + PB + 1;
+    for (int e = threadIdx.x; e < 2 * TC * fill; e += blockDim.x) {
+      const int t = e / fill, w = e % fill;
+      float* tok = sm + (size_t)t * per;
+      if (w < 2 * spare) tok[(w / spare) * dpp + staged_at<NR>(d + w % spare)] = 0.f;
+      else tok[2 * dpp + (w - 2 * spare)] = w - 2 * spare == PB ? 1.f : 0.f;
+    }
+  }
   if (threadIdx.x == 0) ms[0] = mx[(size_t)slot * H + h];
   __syncthreads();
   const float qscale = rsqrtf((float)d);
@@ -270,10 +294,13 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
       floor_[t] = expf(-ms[t + 1]);
     }
     __syncthreads();
-    for (int t = 0; t < nt; ++t) {
-      const float* tok = base + (size_t)t * per;
-      const float4* gq = reinterpret_cast<const float4*>(tok + s * (NR + 4));
-      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + s * (NR + 4));
+    const float* tok = base;
+    const int mine = s * staged_stride<NR>();
+    float* so_at = so + col_local;
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t, tok += per, so_at += PB + 1) {
+      const float4* gq = reinterpret_cast<const float4*>(tok + mine);
+      const float4* gk = reinterpret_cast<const float4*>(tok + dpp + mine);
       const float kp = keep[t], w = take[t] * tok[2 * dpp + cv];
       float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
@@ -285,7 +312,7 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
         p2 = fmaf(S[4 * i + 2], qv.z, p2); p3 = fmaf(S[4 * i + 3], qv.w, p3);
       }
       const float po = group_sum((p0 + p1) + (p2 + p3), NS) * qscale;
-      if (s == 0 && col_local <= PB) so[(size_t)t * (PB + 1) + col_local] = po;
+      if (s == 0 && col_local <= PB) *so_at = po;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < nt * PB; e += blockDim.x) {
@@ -331,25 +358,36 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, 
   }
 }
 
-// (threads per value column, state rows per thread) for d key channels
-bool split_rows(int d, int* ns_out, int* nr_out) {
+int round_nr(int nr) { return nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32; }
+
+// (threads per value column, state rows per thread) for d key channels and `columns` value columns in the whole
+// launch. A column's chain of arithmetic per token is serial, so a launch with few columns (one prompt) is bound by
+// latency: it gets more threads per column, down to four state rows each, until the GPU's schedulers have several
+// warps apiece; a launch with many columns (a batch of single tokens) keeps longer rows per thread.
+bool split_rows(int d, long long columns, int* ns_out, int* nr_out) {
   int ns = 1;
   while ((d + ns - 1) / ns > MAXR && ns < 32) ns <<= 1;
   if ((d + ns - 1) / ns > MAXR) return false;
-  while (ns < 8 && ns * 8 <= d) ns <<= 1;  // shorter chains per thread: at least eight rows each, up to eight threads
+  int sms = 148, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  static const int forced = getenv("CUCA_SCAN_THREADS") ? atoi(getenv("CUCA_SCAN_THREADS")) : 0;  // a measuring aid
+  while (ns < 32 && ns * 4 <= d && (forced ? ns < forced : columns * ns < (long long)sms * 2048)) ns <<= 1;
   *ns_out = ns;
-  *nr_out = (d + ns - 1) / ns;
+  *nr_out = round_nr((d + ns - 1) / ns);
   return true;
 }
 
-int round_nr(int nr) { return nr <= 4 ? 4 : nr <= 8 ? 8 : nr <= 16 ? 16 : 32; }
+// threads of a block: 512 where a column has 16 threads or more (the block's staged vectors then serve more
+// columns), else 128
+int block_threads(int ns, int nr) { return ns >= 16 ? (nr >= 16 ? 256 : 512) : 128; }
 
 }  // namespace
 
 CUCA_API int cuca_matrix_state_max_dim() { return 32 * MAXR; }
 
 // qkv, a_raw and the gate column of b_raw are rewritten in place by the preparing kernel (see there), then scanned.
-CUCA_API int cuca_delta_scan(float* qkv, int ld, float* a_raw, const float* dt_bias, const float* a_log,
+CUCA_API int cuca_delta_scan(float* qkv, int ld, float* a_raw, int ld_a, const float* dt_bias, const float* a_log,
                              float* b_raw, int ld_b, int b_col, float* state, float* out, const int* seq_of_row,
                              const int* req_row0, const int* req_count, const int* slots, int n_rows, int n_seqs, int H,
                              int G, int d, int dv, cudaStream_t stream) {
@@ -358,25 +396,24 @@ CUCA_API int cuca_delta_scan(float* qkv, int ld, float* a_raw, const float* dt_b
                H, G, d, dv);
   CUCA_REQUIRE(n_seqs <= 65535 && H <= 256, "delta_scan: %d requests or %d heads exceed the launch limits", n_seqs, H);
   int ns, nr;
-  CUCA_REQUIRE(split_rows(d, &ns, &nr), "delta_scan: %d key channels exceed %d", d, 32 * MAXR);
-  nr = round_nr(nr);
-  cuca_launch(delta_prepare_kernel, dim3(n_rows), dim3(256), 0, stream, true, qkv, ld, a_raw, dt_bias, a_log, b_raw, ld_b,
+  CUCA_REQUIRE(split_rows(d, (long long)n_seqs * H * dv, &ns, &nr), "delta_scan: %d key channels exceed %d", d, 32 * MAXR);
+  cuca_launch(delta_prepare_kernel, dim3(n_rows), dim3(256), 0, stream, true, qkv, ld, a_raw, ld_a, dt_bias, a_log, b_raw, ld_b,
               b_col, seq_of_row, H, G, d);
   CUCA_CHECK_LAUNCH("delta_prepare");
-  int pb = 128 / ns;
+  int pb = block_threads(ns, nr) / ns;
   pb = pb > dv ? dv : pb;
   const int threads = (pb * ns + 31) / 32 * 32;
-  const int per = (3 * ns * (nr + 4) + pb + 1 + 3) & ~3;
+  const int per = (3 * ns * (nr == 4 ? 4 : nr + 4) + pb + 1 + 3) & ~3;
   int tc = 46000 / (2 * per * 4);
   tc = tc > 16 ? 16 : tc;
   CUCA_REQUIRE(tc >= 1, "delta_scan: a token of %d key channels does not fit shared memory", d);
   const size_t smem = (size_t)2 * tc * per * 4;
   // 16-byte copies where every source is aligned for them
-  const int wide = d % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)a_raw & 15) == 0;
+  const int wide = d % 4 == 0 && ld % 4 == 0 && ld_a % 4 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)a_raw & 15) == 0;
   dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
 #define DS(NR)                                                                                                    \
   cuca_launch(delta_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)qkv, ld,              \
-              (const float*)a_raw, (const float*)b_raw, ld_b, b_col, state, out, req_row0, req_count, slots, H, G, d, \
+              (const float*)a_raw, ld_a, (const float*)b_raw, ld_b, b_col, state, out, req_row0, req_count, slots, H, G, d, \
               dv, ns, pb, tc, wide)
   if (nr == 4) DS(4);
   else if (nr == 8) DS(8);
@@ -397,15 +434,14 @@ CUCA_API int cuca_mlstm_scan(float* proj, int ld, int q_col, int k_col, int v_co
                (double)cap);
   CUCA_REQUIRE(n_seqs <= 65535, "mlstm_scan: %d requests exceed the launch limit", n_seqs);
   int ns, nr;
-  CUCA_REQUIRE(split_rows(d, &ns, &nr), "mlstm_scan: %d key channels exceed %d", d, 32 * MAXR);
-  nr = round_nr(nr);
+  CUCA_REQUIRE(split_rows(d, (long long)n_seqs * H * dv, &ns, &nr), "mlstm_scan: %d key channels exceed %d", d, 32 * MAXR);
   cuca_launch(mlstm_prepare_kernel, dim3((n_rows * H + 127) / 128), dim3(128), 0, stream, true, proj, ld, i_col, f_col,
               i_bias, f_bias, cap, n_rows, H);
   CUCA_CHECK_LAUNCH("mlstm_prepare");
-  int pb = 128 / ns - 1;  // one more column carries n
+  int pb = block_threads(ns, nr) / ns - 1;  // one more column carries n
   pb = pb < 1 ? 1 : (pb > dv ? dv : pb);
   const int threads = ((pb + 1) * ns + 31) / 32 * 32;
-  const int per = (2 * ns * (nr + 4) + (pb + 1) + 2 + 3) & ~3;
+  const int per = (2 * ns * (nr == 4 ? 4 : nr + 4) + (pb + 1) + 2 + 3) & ~3;
   int tc = 46000 / ((2 * per + pb + 6) * 4);
   tc = tc > 16 ? 16 : tc;
   CUCA_REQUIRE(tc >= 1, "mlstm_scan: a token of %d key channels does not fit shared memory", d);

@@ -876,7 +876,8 @@ def delta_scan(qkv, a_raw, dt_bias, a_log, b_src, b_col, state, out, step, H, G,
     decays, the write gate) before the scan; two launches."""
     _cuda(qkv, a_raw, dt_bias, a_log, b_src, state, out)
     library.check(library.load().cuca_delta_scan(
-        _p(qkv), qkv.stride(0), _p(a_raw), _p(dt_bias), _p(a_log), _p(b_src), b_src.stride(0), int(b_col), _p(state),
+        _p(qkv), qkv.stride(0), _p(a_raw), a_raw.stride(0), _p(dt_bias), _p(a_log), _p(b_src), b_src.stride(0), int(b_col),
+        _p(state),
         _p(out), _p(step.seq_of_row), _p(step.req_row0), _p(step.req_count), _p(step.slots), qkv.shape[0], step.n_seqs,
         H, G, d, dv, _stream()), "delta_scan")
     library.launches += 1

@@ -153,7 +153,7 @@ class GatedDelta(Mixer):
             raise ValueError(f"gated_delta: {self.dim} key channels exceed {ops.MATRIX_STATE_MAX_DIM}")
         self.qk = self.kv_heads * self.dim
         self.channels = 2 * self.qk + self.heads * self.vdim
-        self.w_in = self.w_low = self.w_a2 = self.w_g2 = self.conv_w = self.dt_bias = self.a_log = None
+        self.w_in = self.w_low = self.w_2 = self.w_a2 = self.w_g2 = self.conv_w = self.dt_bias = self.a_log = None
         self.norm_w = self.w_o = None
 
     def cache_needs(self):
@@ -183,11 +183,17 @@ class GatedDelta(Mixer):
             raise ValueError(f"gated_delta: `{t['a2']}` / `{t['g2']}` do not continue `{t['a1']}` / `{t['g1']}`: ranks "
                              f"{self.w_a2.shape[1]}, {self.w_g2.shape[1]} against {self.decay_rank}, {self.gate_rank}")
         self.w_low = torch.cat([a1, g1], dim=0).contiguous()
+        # the two second factors as one block-diagonal matrix: [a | gate] = [a1 h | g1 h] W2^T in one contraction
+        w2 = torch.zeros(self.w_a2.shape[0] + self.w_g2.shape[0], self.decay_rank + self.gate_rank,
+                         dtype=self.w_a2.dtype, device=self.w_a2.device)
+        w2[:self.w_a2.shape[0], :self.decay_rank] = self.w_a2
+        w2[self.w_a2.shape[0]:, self.decay_rank:] = self.w_g2
+        self.w_2 = w2
         self.conv_w = torch.cat([get(t["q_conv"]), get(t["k_conv"]), get(t["v_conv"])], dim=0).contiguous()
         self.dt_bias, self.a_log, self.norm_w, self.w_o = get(t["dt_bias"]), get(t["A_log"]), get(t["norm"]), get(t["o"])
 
     def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_low, self.w_a2, self.w_g2, self.conv_w,
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_low, self.w_2, self.conv_w,
                                                           self.dt_bias, self.a_log, self.norm_w, self.w_o))
 
     def forward(self, h, stream, step, cache) -> None:
@@ -195,8 +201,8 @@ class GatedDelta(Mixer):
         H, G, d, dv, C = self.heads, self.kv_heads, self.dim, self.vdim, self.channels
         proj = rt.linear(h, self.w_in, out_dtype=torch.float32)  # [q | k | v | b]
         low = rt.linear(h, self.w_low)  # [a1 h | g1 h], rounded as everything is that enters a contraction
-        a_raw = rt.linear(low[:, :self.decay_rank], self.w_a2, out_dtype=torch.float32)
-        gate = rt.linear(low[:, self.decay_rank:], self.w_g2, out_dtype=torch.float32)
+        second = rt.linear(low, self.w_2, out_dtype=torch.float32)  # [decay pre-activations | gate pre-activations]
+        a_raw, gate = second[:, :H * d], second[:, H * d:]
         qkv = rt.empty(rows, C, dtype=torch.float32)
         ops.causal_conv(proj, 0, self.conv_w, None, cache.state["conv"], qkv, step)
         o = rt.empty(rows, H * dv, dtype=torch.float32)
