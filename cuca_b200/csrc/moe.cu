@@ -29,7 +29,8 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int* _
     int be = 0x7fffffff;
     for (int k = 0; lane + 32 * k < E; ++k) {
       const int e = lane + 32 * k;
-      const float v = z[e];
+      float v = z[e];
+      v = v == v ? v : -INFINITY;  // a row of padding may hold anything: every lane must still see one order
       if (!((taken >> k) & 1u) && (v > best || (v == best && e < be) || be == 0x7fffffff)) { best = v; be = e; }
     }
 #pragma unroll
@@ -38,8 +39,8 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int* _
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
       if (oe != 0x7fffffff && (be == 0x7fffffff || ov > best || (ov == best && oe < be))) { best = ov; be = oe; }
     }
-    if ((be & 31) == lane) taken |= 1u << (be >> 5);
-    if (lane == j) { my_z = best; my_e = be; }
+    if (be < E && (be & 31) == lane) taken |= 1u << (be >> 5);
+    if (lane == j) { my_z = best; my_e = be < E ? be : 0; }
   }
   const float zmax = __shfl_sync(0xffffffffu, my_z, 0);
   const float p = lane < top ? expf(my_z - zmax) : 0.f;
@@ -68,6 +69,32 @@ __global__ void moe_act_dense_kernel(const T* __restrict__ u, const float* __res
   }
 }
 
+// A warp's dot product of two rows of n values: 16 bytes a lane at a time where the rows allow it.
+__device__ __forceinline__ float warp_dot(const float* w, const float* x, int n, int lane) {
+  float acc = 0.f;
+  for (int i = lane; i < n; i += 32) acc = fmaf(w[i], x[i], acc);
+  return warp_sum(acc);
+}
+__device__ __forceinline__ float warp_dot(const __nv_bfloat16* w, const __nv_bfloat16* x, int n, int lane) {
+  float acc = 0.f;
+  if (n % 8 == 0 && ((((uintptr_t)w) | ((uintptr_t)x)) & 15) == 0) {
+    for (int i = lane * 8; i < n; i += 256) {
+      const uint4 a = *reinterpret_cast<const uint4*>(w + i), b = *reinterpret_cast<const uint4*>(x + i);
+      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fa = __bfloat1622float2(pa[k]), fb = __bfloat1622float2(pb[k]);
+        acc = fmaf(fa.x, fb.x, acc);
+        acc = fmaf(fa.y, fb.y, acc);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc = fmaf(__bfloat162float(w[i]), __bfloat162float(x[i]), acc);
+  }
+  return warp_sum(acc);
+}
+
 // a[pair, f] = relu(W_up[e(pair)][f] . h[t])^2 * weight(pair); pair = t * top + j. W_up: [E F, K].
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -80,9 +107,7 @@ moe_up_sparse_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const 
   const int e = idx[pair];
   const T* wr = w_up + ((size_t)e * F + f) * K;
   const T* hr = h + (size_t)(pair / top) * K;
-  float acc = 0.f;
-  for (int i = lane; i < K; i += 32) acc = fmaf(to_f32(wr[i]), to_f32(hr[i]), acc);
-  acc = warp_sum(acc);
+  const float acc = warp_dot(wr, hr, K, lane);
   if (lane == 0) {
     const float v = fmaxf(acc, 0.f);
     a[(size_t)pair * F + f] = from_f32<T>(v * v * wts[pair]);
@@ -103,9 +128,7 @@ moe_down_sparse_kernel(const T* __restrict__ a, const T* __restrict__ w_down, co
     const int e = idx[(size_t)t * top + j];
     const T* wr = w_down + (size_t)o * E * F + (size_t)e * F;
     const T* ar = a + ((size_t)t * top + j) * F;
-    float part = 0.f;
-    for (int i = lane; i < F; i += 32) part = fmaf(to_f32(wr[i]), to_f32(ar[i]), part);
-    acc += warp_sum(part);
+    acc += warp_dot(wr, ar, F, lane);
   }
   if (lane == 0) y[(size_t)t * N + o] = store ? acc : y[(size_t)t * N + o] + acc;
 }

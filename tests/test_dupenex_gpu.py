@@ -276,6 +276,28 @@ def test_routed_experts_alone(rt32, mlp, E):
         assert np.abs(y.data.cpu().numpy() - want).max() < 3e-5 * max(1.0, np.abs(want).max())
 
 
+def test_routing_of_rows_that_hold_anything(rt32):
+    """A captured step's padding rows hold whatever was in memory: the chosen experts must be experts all the same,
+    and distinct ones, since their numbers index the experts' weights."""
+    from cuca_b200.kernels import ops
+    dev = rt32.device
+    z = torch.randn(6, 8, device=dev)
+    z[1] = float("nan")
+    z[2, 3:] = float("nan")
+    z[3] = float("inf")
+    z[4] = float("-inf")
+    z[5] = 0.0
+    for top in (1, 2, 8):
+        idx = torch.full((6, top), -7, dtype=torch.int32, device=dev)
+        wts = torch.empty(6, top, device=dev)
+        ops.moe_route(z, top, idx, wts)
+        got = idx.cpu().numpy()
+        assert ((got >= 0) & (got < 8)).all()
+        assert all(len(set(row)) == top for row in got.tolist())
+        assert got[5].tolist() == list(range(top))  # ties go to the lower number
+        assert np.isfinite(wts[0].cpu().numpy()).all()
+
+
 # ------------------------------------------------------------------------------------------ whole models
 LENGTHS = {"mix": [1, 2, 5, 16, 33, 64, 97, 130], "plain": [3, 17, 48, 100], "one": [1, 18, 35, 77],
            "wide": [1, 15, 33, 34, 65, 140], "two": [2, 40, 90]}
