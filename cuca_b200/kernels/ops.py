@@ -889,7 +889,7 @@ def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem
         _p(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(i_col), int(f_col), _p(i_bias), _p(f_bias),
         float(cap), _p(mem), _p(nrm), _p(mx), _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots),
         proj.shape[0], step.n_seqs, H, d, dv, _stream()), "mlstm_scan")
-    library.launches += 1  # the gates are prepared by a launch of their own
+    library.launches += 2  # the gates are prepared by a launch of their own, the new n and m left by another
 
 
 def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:

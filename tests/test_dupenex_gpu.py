@@ -150,6 +150,30 @@ def test_matrix_memory_alone_whole_and_cut(rt32, right):
             assert np.abs(a - b).max() < 3e-5 * max(1.0, np.abs(b).max())
 
 
+def test_matrix_memory_more_blocks_than_the_gpu_holds(rt32):
+    """Forty requests of wide heads in one step: far more blocks than are resident at once, so the last blocks of a
+    (head, request) start when its first ones are done. All of them must still start from the same normaliser and
+    running maximum, which the step replaces only after every block has read them."""
+    from cuca_b200.cache.device import CacheView
+    dev, E, eps, R = rt32.device, 24, 1e-5, 40
+    layer = du.par(r_heads=4, r_dim=16, r_vdim=520, cap=4.0)
+    part = _mixer(layer, rt32, E, eps).sides["right"]
+    ws = _mixer_weights(part, 21)
+    _load(part, ws, dev)
+    rs = np.random.default_rng(22)
+    xs = [rs.normal(0, 1.5, (4, E)) for _ in range(R)]
+    want = [pd.matrix_memory(x, ws, "l0.mix.right.", layer["mixer"]["right"], eps) for x in xs]
+    state = {k: torch.zeros(R, *v.shape, device=dev) for k, v in part.cache_needs().state.items()}
+
+    def fwd(h, step):
+        out = torch.zeros(h.shape[0], E, device=dev)
+        part.forward(h, out, step, CacheView(None, None, None, 16, -1, state, step.slots))
+        return out
+    got = _run_cut(dev, fwd, xs, [[1, 1, 2]] * R, list(range(R)), E)
+    for a, b in zip(got, want):
+        assert np.abs(a - b).max() < 3e-5 * max(1.0, np.abs(b).max())
+
+
 ATTENTIONS = [du.par(window=12), du.par(window=None, dims=0, heads=3, kv_heads=3),
               du.par(heads=1, kv_heads=1, dim=32, vdim=16, window=1, dims=32),
               du.par(heads=6, kv_heads=2, dim=12, vdim=10, window=16, dims=6, scale=1.2, base=250000.0),
