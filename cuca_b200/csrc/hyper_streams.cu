@@ -11,7 +11,7 @@
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 // Blocks of NT threads take one row each; a thread works on V consecutive columns at a time (V = 4: 16-byte
 // accesses, for widths that are multiples of four). Few rows (single tokens) get blocks of 1,024 threads, so that a

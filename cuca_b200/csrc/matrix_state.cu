@@ -209,14 +209,13 @@ __global__ void mlstm_prepare_kernel(float* __restrict__ proj, int ld, int i_col
 // The block's columns are its PB value columns and one more that carries n (its "value" is 1), so n . q comes out
 // of the same loop; the division waits until the chunk's sums are in shared memory. q enters unscaled: the sums
 // are linear in it, so d^(-1/2) multiplies them afterwards. n and m are shared by all blocks of a (head, request):
-// the launch over the value columns only reads them, a second launch with PB = 0 and write_nm set walks the same
-// tokens with the n column alone and leaves the new n and m.
+// this launch only reads them and leaves the new ones aside (nm_new); `mlstm_commit_kernel` moves them into the slots.
 template <int NR>
 __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int i_col,
                                   int f_col, float* __restrict__ mem, float* __restrict__ nrm, float* __restrict__ mx,
                                   float* __restrict__ out, const int* __restrict__ req_row0,
                                   const int* __restrict__ req_count, const int* __restrict__ slots, int H, int d,
-                                  int dv, int NS, int PB, int TC, int wide, int write_nm) {
+                                  int dv, int NS, int PB, int TC, int wide, float* __restrict__ nm_new) {
   extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
@@ -328,13 +327,32 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_
     __syncthreads();  // the buffers and the chunk's sums are free again
   }
   // every block of a (head, request) starts from the same n and m, so no block of this launch may replace them:
-  // a launch of its own (no value columns, write_nm set) does that once this one is through
-  if (live && col_local <= PB && (!is_n || write_nm)) {
+  // the block of the first columns leaves the new ones in nm_new [requests, H, d + 1], and a launch of its own
+  // moves them into the slots once this one is through
+  if (live && col_local < PB) {
 #pragma unroll
     for (int i = 0; i < NR; ++i)
       if (s * NR + i < d) st[s * NR + i] = S[i];
   }
-  if (threadIdx.x == 0 && write_nm) mx[(size_t)slot * H + h] = ms[0];
+  float* nm = nm_new + ((size_t)rq * H + h) * (d + 1);
+  if (is_n && blockIdx.z == 0) {
+#pragma unroll
+    for (int i = 0; i < NR; ++i)
+      if (s * NR + i < d) nm[s * NR + i] = S[i];
+  }
+  if (threadIdx.x == 0 && blockIdx.z == 0) nm[d] = ms[0];
+}
+
+__global__ void mlstm_commit_kernel(const float* __restrict__ nm_new, float* __restrict__ nrm, float* __restrict__ mx,
+                                    const int* __restrict__ req_count, const int* __restrict__ slots, int H, int d) {
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, rq = blockIdx.y;
+  const int slot = slots[rq];
+  if (slot < 0 || req_count[rq] <= 0) return;
+  const float* nm = nm_new + ((size_t)rq * H + h) * (d + 1);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) nrm[((size_t)slot * H + h) * d + i] = nm[i];
+  if (threadIdx.x == 0) mx[(size_t)slot * H + h] = nm[d];
 }
 
 // o: [rows, H dv] 32-bit. out[r, h, j] = o / sqrt(mean_j o^2 + eps) * w[h * w_head + j] * sigmoid(gate[r, h dv + j]);
@@ -429,10 +447,11 @@ CUCA_API int cuca_delta_scan(float* qkv, int ld, float* a_raw, int ld_a, const f
 }
 
 // The two gate columns of proj are rewritten in place by the preparing kernel (see there), then scanned.
+// nm_new: scratch of n_seqs * H * (d + 1) floats.
 CUCA_API int cuca_mlstm_scan(float* proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                              const float* i_bias, const float* f_bias, float cap, float* mem, float* nrm, float* mx,
-                             float* out, const int* req_row0, const int* req_count, const int* slots, int n_rows,
-                             int n_seqs, int H, int d, int dv, cudaStream_t stream) {
+                             float* out, float* nm_new, const int* req_row0, const int* req_count, const int* slots,
+                             int n_rows, int n_seqs, int H, int d, int dv, cudaStream_t stream) {
   if (n_seqs == 0 || n_rows == 0) return 0;
   CUCA_REQUIRE(H > 0 && d > 0 && dv > 0 && cap > 0.f, "mlstm_scan: bad sizes heads=%d dim=%d vdim=%d cap=%g", H, d, dv,
                (double)cap);
@@ -452,26 +471,18 @@ CUCA_API int cuca_mlstm_scan(float* proj, int ld, int q_col, int k_col, int v_co
   const size_t smem = ((size_t)2 * tc * per + (size_t)tc * (pb + 1) + 4 * tc + 1) * 4;
   const int wide = d % 4 == 0 && ld % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && ((uintptr_t)proj & 15) == 0;
   dim3 grid(H, n_seqs, (dv + pb - 1) / pb);
-  // the n column alone: what the second launch (the new n and m) needs
-  const int per0 = (2 * ns * (nr == 4 ? 4 : nr + 4) + 1 + 2 + 3) & ~3;
-  int tc0 = 46000 / ((2 * per0 + 6) * 4);
-  tc0 = tc0 > 16 ? 16 : tc0;
-  const size_t smem0 = ((size_t)2 * tc0 * per0 + (size_t)tc0 + 4 * tc0 + 1) * 4;
-  const int threads0 = (ns + 31) / 32 * 32;
 #define MS(NR)                                                                                                      \
-  do {                                                                                                              \
-    cuca_launch(mlstm_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, k_col, \
-                v_col, i_col, f_col, mem, nrm, mx, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide, 0);   \
-    cuca_launch(mlstm_scan_kernel<NR>, dim3(H, n_seqs, 1), dim3(threads0), smem0, stream, true, (const float*)proj,   \
-                ld, q_col, k_col, v_col, i_col, f_col, mem, nrm, mx, out, req_row0, req_count, slots, H, d, dv, ns, 0, \
-                tc0, wide, 1);                                                                                      \
-  } while (0)
+  cuca_launch(mlstm_scan_kernel<NR>, grid, dim3(threads), smem, stream, true, (const float*)proj, ld, q_col, k_col,   \
+              v_col, i_col, f_col, mem, nrm, mx, out, req_row0, req_count, slots, H, d, dv, ns, pb, tc, wide, nm_new)
   if (nr == 4) MS(4);
   else if (nr == 8) MS(8);
   else if (nr == 16) MS(16);
   else MS(32);
 #undef MS
   CUCA_CHECK_LAUNCH("mlstm_scan");
+  cuca_launch(mlstm_commit_kernel, dim3(H, n_seqs), dim3(128), 0, stream, true, (const float*)nm_new, nrm, mx, req_count,
+              slots, H, d);
+  CUCA_CHECK_LAUNCH("mlstm_commit");
   return 0;
 }
 

@@ -97,7 +97,7 @@ _SIGNATURES = {
     "cuca_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
     "cuca_matrix_state_max_dim": [],
     "cuca_delta_scan": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "cuca_mlstm_scan": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "cuca_mlstm_scan": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "cuca_head_norm_gate": [_P, _P, _I, _P, _I, _I, _P, _I, _I, _I, _I, _F, _P],
     "cuca_moe_max_experts": [],
     "cuca_moe_route": [_P, _I, _I, _I, _P, _P, _P, _P],

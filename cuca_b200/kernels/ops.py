@@ -831,7 +831,7 @@ def gate_merge(parts, gate, out, n_heads, v_head_dim) -> None:
 
 
 # ------------------------------------------------------------------ several copies of the residual stream
-STREAMS_MAX = 8  # `cuca_streams_max` says the same
+STREAMS_MAX = 16  # `cuca_streams_max` says the same
 
 
 def spread_streams(x, X, copies: int) -> None:
@@ -885,11 +885,13 @@ def delta_scan(qkv, a_raw, dt_bias, a_log, b_src, b_col, state, out, step, H, G,
 
 def mlstm_scan(proj, q_col, k_col, v_col, i_col, f_col, i_bias, f_bias, cap, mem, nrm, mx, out, step, H, d, dv) -> None:
     _cuda(proj, mem, nrm, mx, out)
+    # the new normaliser and running maximum of every (request, head), set aside until every block has read the old
+    aside = torch.empty(step.n_seqs * H * (d + 1), dtype=torch.float32, device=out.device)
     library.check(library.load().cuca_mlstm_scan(
         _p(proj), proj.stride(0), int(q_col), int(k_col), int(v_col), int(i_col), int(f_col), _p(i_bias), _p(f_bias),
-        float(cap), _p(mem), _p(nrm), _p(mx), _p(out), _p(step.req_row0), _p(step.req_count), _p(step.slots),
+        float(cap), _p(mem), _p(nrm), _p(mx), _p(out), _p(aside), _p(step.req_row0), _p(step.req_count), _p(step.slots),
         proj.shape[0], step.n_seqs, H, d, dv, _stream()), "mlstm_scan")
-    library.launches += 2  # the gates are prepared by a launch of their own, the new n and m left by another
+    library.launches += 2  # the gates are prepared by a launch of their own, the new n and m moved in by another
 
 
 def head_norm_gate(o, weight, per_head: bool, gate, out, H, dv, eps) -> None:

@@ -24,7 +24,7 @@ def _f32(a, dev):
 
 
 # ------------------------------------------------------------------------------------------ mechanisms alone
-@pytest.mark.parametrize("S, E", [(1, 40), (3, 52), (5, 300), (8, 33)])
+@pytest.mark.parametrize("S, E", [(1, 40), (3, 52), (5, 300), (8, 33), (16, 64), (11, 2052)])
 def test_stream_copies_read_and_write(rt32, S, E):
     from cuca_b200.kernels import ops
     dev, eps, rows = rt32.device, 1e-5, 7
