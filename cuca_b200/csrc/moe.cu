@@ -1,6 +1,6 @@
 // A routed feed-forward: every token goes to the `top` experts with the largest router logits.
 //   moe_route        per token: the chosen experts (largest logit first, the lower number on a tie), their weights
-//                    (softmax over the chosen logits alone) and, optionally, the weights spread over all experts
+//                    (a softmax of just those logits) and, optionally, the weights spread over all experts
 //   moe_act_dense    a[t, e, f] = relu(u[t, e, f])^2 * weight[t, e]: all experts' up-projections at once, the ones a
 //                    token did not choose weighted 0, so that one contraction over (e, f) is the weighted sum
 //   moe_up_sparse / moe_down_sparse   few tokens: only the chosen experts' weights are read, a warp per output

@@ -5,8 +5,8 @@ layers carry that many copies of the residual stream (`hyper_connections` blocks
 the copies and writes into all of them; the model's output is the copies' sum), else the plain pre-norm residual.
 Mixers: `channel_delta` (the `gated_delta` part: a delta rule with a decay per key channel behind short convolutions)
 and `parallel` (the `parallel` part around a sliding-window `attention` with rotary adjacent pairs, value heads of
-their own size and an output gate, and an `mlstm` matrix memory; each side's output is normed, the result is half
-their sum). Feed-forwards: dense SwiGLU, or `routed` experts with a squared-relu activation. A stretch of layers
+their own size and an output gate, and an `mlstm` matrix memory; each side's output is normed and the two are
+averaged). Feed-forwards: dense SwiGLU, or `routed` experts with a squared-relu activation. A stretch of layers
 may run several passes in a row with the same weights, each run with a cache and state of its own, nothing between.
 Tensor names: `embed`, `head`, `final.norm` and per layer i `l<i>.norm1|norm2`, `l<i>.hc1|hc2.in|out|mix`,
 `l<i>.mix.*`, `l<i>.mlp.*`.

@@ -85,7 +85,7 @@ class DenseActivation(FeedForward):
 @register_feed_forward("routed")
 class RoutedExperts(FeedForward):
     """Every token goes to the `top` of `experts` small feed-forwards with the largest router logits z = W_r f
-    (32-bit), weighted by the softmax over the chosen logits alone: y = sum_e p_e down_e(act(up_e f)), act the
+    (32-bit), with weights p = softmax of just those `top` logits: y = sum_e p_e down_e(act(up_e f)), act the
     square of relu. The experts' weights are stacked at load (`up` [experts * inner, width], `down` [width,
     experts * inner]). Many tokens: all experts' up-projections in one contraction, the activation weighted per
     expert (0 for the ones a token did not choose), one contraction over (expert, inner) down. Few tokens: only the

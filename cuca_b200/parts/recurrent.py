@@ -127,7 +127,7 @@ class GatedDelta(Mixer):
     become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q times dim^(-1/2); head a reads q/k head
     a // (heads / kv_heads). beta = sigmoid(W_b h) per head;
     g = exp(-exp(A_log[a]) * softplus(W_a2 (W_a1 h) + dt_bias)) per head and key channel. Per head, S of dim x vdim:
-        S <- g[:, None] * S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (the read-out sees the write).
+        S <- g[:, None] * S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q   (q reads S after the token's own update).
     o / rms(o) per head, times `norm` [vdim], times sigmoid(W_g2 (W_g1 h)), then W_o. The ranks of the two low-rank
     pairs are the stored tensors' (`decay_rank`, `gate_rank` only size random weights).
     The state is S (32-bit) and the convolution's last taps - 1 inputs.
